@@ -22,7 +22,7 @@ from dataclasses import dataclass, field
 
 import numpy as np
 
-from emberserve_b200.parts.base import CacheNeed, FixedState, PagedKV
+from emberserve_b200.parts.base import CacheNeed
 
 
 class OutOfPages(RuntimeError):
@@ -36,7 +36,7 @@ class CacheGroup:
 
     @property
     def paged(self) -> bool:
-        return isinstance(self.need, PagedKV)
+        return bool(self.need.paged)
 
 
 def plan_groups(entries: list[CacheNeed]) -> list[CacheGroup]:

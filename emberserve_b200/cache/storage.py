@@ -2,7 +2,8 @@
 
 A paged group with E entries holds one tensor ``[E, 2, num_pages, kv_heads, page_size,
 head_dim]`` (2 = keys, values), so the keys of one (page, KV head) are one contiguous tile
-of ``page_size * head_dim`` elements.  The reference keeps ``[num_blocks, block_size,
+of ``page_size * head_dim`` elements; a group of latent vectors (``PagedLatent``) holds
+``[E, num_pages, page_size, dim]``.  The reference keeps ``[num_blocks, block_size,
 kv_heads, head_dim]`` per layer (``emberserve/kv/cache.py:30-34``); the geometry (pages of
 ``block_size`` token slots, slot = page * page_size + offset) is the same.  Contents are
 never cleared when pages change hands.  A state group holds ``[E, num_slots, *shape]``,
@@ -14,7 +15,8 @@ from __future__ import annotations
 import torch
 
 from emberserve_b200.cache.manager import CacheGroup
-from emberserve_b200.parts.base import FixedState, FixedStateHandle, PagedKV, PagedKVHandle
+from emberserve_b200.parts.base import (FixedState, FixedStateHandle, PagedKV, PagedKVHandle, PagedLatent,
+                                        PagedLatentHandle)
 
 _STATE_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "int32": torch.int32}
 
@@ -31,10 +33,14 @@ class CacheStorage:
         self.where: dict[int, tuple[int, int, int]] = {}
         paged_seen = 0
         for gi, g in enumerate(groups):
-            if isinstance(g.need, PagedKV):
+            if g.need.paged:
                 n = num_pages[paged_seen]
-                t = torch.zeros(len(g.entries), 2, n, g.need.num_kv_heads, page_size, g.need.head_dim,
-                                dtype=dtype, device=self.device)
+                if isinstance(g.need, PagedLatent):
+                    t = torch.zeros(len(g.entries), n, page_size, g.need.dim, dtype=dtype, device=self.device)
+                else:
+                    assert isinstance(g.need, PagedKV)
+                    t = torch.zeros(len(g.entries), 2, n, g.need.num_kv_heads, page_size, g.need.head_dim,
+                                    dtype=dtype, device=self.device)
                 for j, e in enumerate(g.entries):
                     self.where[e] = (gi, j, paged_seen)
                 paged_seen += 1
@@ -68,14 +74,21 @@ class CacheStorage:
             if not g.paged:
                 t.index_fill_(1, idx, 0)
 
-    def handle(self, entry: int, write: bool, block_tables: list[torch.Tensor],
-               slots: torch.Tensor | None) -> PagedKVHandle | FixedStateHandle:
+    def handle(self, entry: "int | tuple[int, ...]", write: bool, block_tables: list[torch.Tensor],
+               slots: torch.Tensor | None):
+        """The handle of one cache entry for a step; for a tuple of entries (a block that keeps
+        several things) the tuple of their handles."""
+        if isinstance(entry, tuple):
+            return tuple(self.handle(e, write, block_tables, slots) for e in entry)
         gi, j, pk = self.where[entry]
         need = self.groups[gi].need
         t = self.tensors[gi]
         if isinstance(need, PagedKV):
             return PagedKVHandle(k=t[j, 0], v=t[j, 1], block_tables=block_tables[pk],
                                  page_size=self.page_size, window=need.window, write=write)
+        if isinstance(need, PagedLatent):
+            return PagedLatentHandle(pages=t[j], block_tables=block_tables[pk], page_size=self.page_size,
+                                     window=need.window, write=write)
         return FixedStateHandle(state=t[j], slots=slots, write=write)
 
     def reset(self) -> None:

@@ -1,0 +1,250 @@
+// Row-wise kernels around the residual stream for decoders with a norm on both sides of every
+// sub-layer: a vector added to the stream between layers, the grouped RMSNorm fused with the
+// norm of the delta that joins the stream before it, gated activations other than SiLU, and
+// the short causal convolution over time with its per-request state.
+//
+// All arithmetic is 32-bit; the storage type T is float (the true 32-bit path) or bfloat16.
+//
+//   grouped RMSNorm   the vector is cut into G equal consecutive parts; part g is divided by
+//                     sqrt(mean(part^2) + eps); the whole is multiplied by the gain.  Nothing
+//                     is rounded between the division and the gain.
+//   post + pre norm   residual += norm_post(delta);  out = norm_pre(residual)
+//   causal taps       out[t] = h[t] + sum_j w[:, j] * h[t - taps + 1 + j], h = 0 before the
+//                     request's first token; the last taps - 1 inputs of a request are its state
+#include "common.cuh"
+
+namespace ems {
+
+// ---------------------------------------------------------------------------------------
+// residual[n, :] += embed[tokens[n], :] + table[row, :]   (either may be absent)
+
+template <typename T>
+__global__ void stream_inject_kernel(float* __restrict__ residual, const int* __restrict__ tokens,
+                                     const int* __restrict__ deferred, const T* __restrict__ embed,
+                                     const T* __restrict__ vec, int H) {
+    const size_t n = blockIdx.x;
+    const T* e = nullptr;
+    if (embed) {
+        int tok = tokens[n];
+        if (tok < 0) tok = deferred ? deferred[-(tok + 1)] : 0;
+        e = embed + (size_t)tok * H;
+    }
+    float* r = residual + n * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float s = r[i];
+        if (e) s += to_f32<T>(e[i]);
+        if (vec) s += to_f32<T>(vec[i]);
+        r[i] = s;
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// One block per output row.  buf (dynamic shared memory) holds the row in 32 bits between the
+// phases, followed by one factor per group.  The order of every sum depends on blockDim and the
+// sizes only.
+
+template <typename T>
+__global__ void add_norm_grouped_kernel(const T* __restrict__ delta, const void* __restrict__ post_gain,
+                                        int pg_dtype, int post_groups, float post_eps, float* residual,
+                                        const void* __restrict__ gain, int g_dtype, int groups, float eps,
+                                        T* __restrict__ out, const int* __restrict__ rows, int H,
+                                        int write_residual) {
+    extern __shared__ float buf[];
+    __shared__ float red[33];
+    float* stat = buf + H;
+    const size_t r = blockIdx.x;
+    const size_t src = rows ? (size_t)rows[r] : r;
+    float* res = residual + src * H;
+    const T* dl = delta ? delta + src * H : nullptr;
+    if (dl && post_gain) {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) buf[i] = to_f32<T>(dl[i]);
+        __syncthreads();
+        const int gs = H / post_groups;
+        for (int g = 0; g < post_groups; ++g) {
+            float ss = 0.f;
+            for (int i = threadIdx.x; i < gs; i += blockDim.x) {
+                const float v = buf[g * gs + i];
+                ss += v * v;
+            }
+            const float total = block_sum(ss, red);
+            if (threadIdx.x == 0) stat[g] = 1.0f / sqrtf(total / (float)gs + post_eps);
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            const float s = res[i] + buf[i] * stat[i / gs] * load_any(post_gain, pg_dtype, i);
+            buf[i] = s;
+            if (write_residual) res[i] = s;
+        }
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            float s = res[i];
+            if (dl) {
+                s += to_f32<T>(dl[i]);
+                if (write_residual) res[i] = s;
+            }
+            buf[i] = s;
+        }
+    }
+    __syncthreads();
+    const int gs = H / groups;
+    for (int g = 0; g < groups; ++g) {
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < gs; i += blockDim.x) {
+            const float v = buf[g * gs + i];
+            ss += v * v;
+        }
+        const float total = block_sum(ss, red);  // (its barriers also order the reads of stat above)
+        if (threadIdx.x == 0) stat[g] = 1.0f / sqrtf(total / (float)gs + eps);
+    }
+    __syncthreads();
+    T* o = out + r * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x)
+        o[i] = from_f32<T>(buf[i] * stat[i / gs] * load_any(gain, g_dtype, i));
+}
+
+// ---------------------------------------------------------------------------------------
+// out[n, i] = act(gu[n, i]) * gu[n, I + i];  act: 0 SiLU, 1 ReLU, 2 GELU (tanh form)
+
+__device__ __forceinline__ float glu_activation(float g, int act) {
+    if (act == 1) return fmaxf(g, 0.f);
+    if (act == 2) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    return g / (1.f + expf(-g));
+}
+
+template <typename T>
+__global__ void glu_act_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, int act) {
+    const size_t n = blockIdx.x;
+    const T* g = gu + n * 2 * I;
+    T* o = out + n * I;
+    for (int i = threadIdx.x; i < I; i += blockDim.x)
+        o[i] = from_f32<T>(glu_activation(to_f32<T>(g[i]), act) * to_f32<T>(g[I + i]));
+}
+
+// ---------------------------------------------------------------------------------------
+// causal taps.  x: [N, C] packed rows; w: [C, taps]; state: [slots, taps - 1, C] float, the last
+// taps - 1 inputs of each request in time order (zero where the request has not begun).
+
+template <typename T>
+__global__ void causal_taps_kernel(const T* __restrict__ x, const void* __restrict__ w, int w_dtype,
+                                   const float* __restrict__ state, const int* __restrict__ slots,
+                                   const int* __restrict__ cu_q, const int* __restrict__ row_of_token,
+                                   T* __restrict__ out, int C, int taps) {
+    const int t = blockIdx.x;
+    const int row = row_of_token[t];
+    const int first = cu_q[row];
+    const int local = t - first;
+    const float* st = state ? state + (size_t)slots[row] * (taps - 1) * C : nullptr;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        float conv = 0.f;
+        for (int j = 0; j < taps; ++j) {
+            const int s = local - (taps - 1) + j;
+            float v;
+            if (s >= 0) v = to_f32<T>(x[(size_t)(first + s) * C + c]);
+            else v = st ? st[(size_t)(taps - 1 + s) * C + c] : 0.f;
+            conv += load_any(w, w_dtype, (size_t)c * taps + j) * v;
+        }
+        out[(size_t)t * C + c] = from_f32<T>(to_f32<T>(x[(size_t)t * C + c]) + conv);
+    }
+}
+
+// After the convolution has read the old state: the last taps - 1 inputs of every row, from the
+// step's tokens and, where the row brought fewer, from the old state moved up.  A thread owns a
+// channel, reads entries above the one it writes, and so needs no second buffer.
+template <typename T>
+__global__ void causal_taps_state_kernel(const T* __restrict__ x, float* __restrict__ state,
+                                         const int* __restrict__ slots, const int* __restrict__ cu_q, int C,
+                                         int taps) {
+    const int row = blockIdx.x;
+    const int first = cu_q[row], q = cu_q[row + 1] - first;
+    if (q <= 0) return;
+    float* st = state + (size_t)slots[row] * (taps - 1) * C;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        for (int s = 0; s < taps - 1; ++s) {
+            const int src = q - (taps - 1) + s;
+            st[(size_t)s * C + c] = src >= 0 ? to_f32<T>(x[(size_t)(first + src) * C + c])
+                                             : st[(size_t)(s + q) * C + c];
+        }
+    }
+}
+
+static int threads_for(int n) {
+    int t = 32;
+    while (t < n && t < 256) t <<= 1;
+    return t;
+}
+
+}  // namespace ems
+
+using namespace ems;
+
+EMS_EXPORT int ems_stream_inject(void* residual, const int* tokens, const int* deferred, const void* embed,
+                                 const void* vec, int dtype, int n, int H, cudaStream_t stream) {
+    if (n <= 0) return EMS_OK;
+    const int th = threads_for(H);
+    if (dtype == EMS_F32)
+        stream_inject_kernel<float><<<n, th, 0, stream>>>((float*)residual, tokens, deferred, (const float*)embed,
+                                                          (const float*)vec, H);
+    else if (dtype == EMS_BF16)
+        stream_inject_kernel<bf16><<<n, th, 0, stream>>>((float*)residual, tokens, deferred, (const bf16*)embed,
+                                                         (const bf16*)vec, H);
+    else
+        return EMS_ERR_DTYPE;
+    return launch_status();
+}
+
+EMS_EXPORT int ems_add_norm_grouped(const void* delta, const void* post_gain, int pg_dtype, int post_groups,
+                                    float post_eps, void* residual, const void* gain, int g_dtype, int groups,
+                                    float eps, void* out, int dtype, const int* rows, int n, int H,
+                                    int write_residual, cudaStream_t stream) {
+    if (n <= 0) return EMS_OK;
+    if (groups <= 0 || H % groups || (post_gain && (post_groups <= 0 || H % post_groups))) return EMS_ERR_SHAPE;
+    const int most = groups > post_groups ? groups : post_groups;
+    const size_t smem = (size_t)(H + most) * sizeof(float);
+    if (smem > 200 * 1024) return EMS_ERR_SHAPE;
+    const int th = threads_for(H);
+#define EMS_LAUNCH_NORM(T)                                                                                     \
+    do {                                                                                                       \
+        if (smem > 48 * 1024)                                                                                  \
+            cudaFuncSetAttribute(add_norm_grouped_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,      \
+                                 (int)smem);                                                                   \
+        add_norm_grouped_kernel<T><<<n, th, smem, stream>>>((const T*)delta, post_gain, pg_dtype, post_groups, \
+                                                            post_eps, (float*)residual, gain, g_dtype, groups, \
+                                                            eps, (T*)out, rows, H, write_residual);            \
+    } while (0)
+    if (dtype == EMS_F32) EMS_LAUNCH_NORM(float);
+    else if (dtype == EMS_BF16) EMS_LAUNCH_NORM(bf16);
+    else return EMS_ERR_DTYPE;
+#undef EMS_LAUNCH_NORM
+    return launch_status();
+}
+
+EMS_EXPORT int ems_glu_act(const void* gu, void* out, int dtype, int n, int I, int act, cudaStream_t stream) {
+    if (n <= 0) return EMS_OK;
+    if (act < 0 || act > 2) return EMS_ERR_SHAPE;
+    const int th = threads_for(I);
+    if (dtype == EMS_F32) glu_act_kernel<float><<<n, th, 0, stream>>>((const float*)gu, (float*)out, I, act);
+    else if (dtype == EMS_BF16) glu_act_kernel<bf16><<<n, th, 0, stream>>>((const bf16*)gu, (bf16*)out, I, act);
+    else return EMS_ERR_DTYPE;
+    return launch_status();
+}
+
+EMS_EXPORT int ems_causal_taps(const void* x, const void* w, int w_dtype, void* state, const int* slots,
+                               const int* cu_q, const int* row_of_token, void* out, int dtype, int n, int rows,
+                               int C, int taps, cudaStream_t stream) {
+    if (n <= 0) return EMS_OK;
+    if (taps < 1 || (taps > 1 && !state)) return EMS_ERR_SHAPE;
+    const int th = threads_for(C);
+#define EMS_LAUNCH_TAPS(T)                                                                                   \
+    do {                                                                                                     \
+        causal_taps_kernel<T><<<n, th, 0, stream>>>((const T*)x, w, w_dtype, (const float*)state, slots,     \
+                                                    cu_q, row_of_token, (T*)out, C, taps);                  \
+        if (taps > 1)                                                                                        \
+            causal_taps_state_kernel<T><<<rows, th, 0, stream>>>((const T*)x, (float*)state, slots, cu_q, C, \
+                                                                 taps);                                      \
+    } while (0)
+    if (dtype == EMS_F32) EMS_LAUNCH_TAPS(float);
+    else if (dtype == EMS_BF16) EMS_LAUNCH_TAPS(bf16);
+    else return EMS_ERR_DTYPE;
+#undef EMS_LAUNCH_TAPS
+    return launch_status();
+}

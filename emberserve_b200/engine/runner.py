@@ -30,7 +30,7 @@ from emberserve_b200.cache.manager import CacheManager, plan_groups
 from emberserve_b200.cache.storage import CacheStorage
 from emberserve_b200.config.model import ModelConfig
 from emberserve_b200.engine.memory import MemoryPlan, plan_memory
-from emberserve_b200.parts.base import PagedKV, StepContext
+from emberserve_b200.parts.base import StepContext
 from emberserve_b200.parts.decoder import Decoder
 from emberserve_b200.parts.linear import strict_matmul_precision
 from emberserve_b200.registry import build_decoder, load_config
@@ -234,8 +234,7 @@ class ModelRunner:
         esize = torch.empty((), dtype=self.dtype).element_size()
         total = 0
         for g in paged:
-            need: PagedKV = g.need
-            total += len(g.entries) * 2 * need.num_kv_heads * self.page_size * need.head_dim * esize
+            total += len(g.entries) * g.need.elements_per_token() * self.page_size * esize
         return total
 
     def _pages_from_free_memory(self, paged, utilization: float, reserve: int | None, max_step_tokens: int,

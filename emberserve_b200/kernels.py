@@ -72,6 +72,18 @@ def _declare(lib: ctypes.CDLL) -> None:
         "ems_gemm_midm": [P, P, P, P, I, I, I, I, I, P],
         "ems_gemm_midm_max_clusters": [I, I],
         "ems_gemm_large_gated": [P, P, P, I, I, I, I, P],
+        "ems_stream_inject": [P, P, P, P, P, I, I, I, P],
+        "ems_add_norm_grouped": [P, P, I, I, F, P, P, I, I, F, P, I, P, I, I, I, P],
+        "ems_glu_act": [P, P, I, I, I, I, P],
+        "ems_causal_taps": [P, P, I, P, P, P, P, P, I, I, I, I, I, P],
+        "ems_latent_prep": [P, I, I, I, I, I, I, P, P, I, F, P, P, P, I, I, P, P, I, I, P, I, P],
+        "ems_rope_inplace": [P, I, I, I, I, I, I, I, I, P, P, P],
+        "ems_latent_attention": [P, P, I, I, I, P, P, I, I, P, P, P, I, I, I, I, F, I, P, L, P],
+        "ems_heads_gate": [P, P, I, P, I, I, I, I, P],
+        "ems_moe_route": [P, I, I, I, I, P, P, P, P, P, I, P],
+        "ems_moe_up": [P, P, I, P, P, I, I, I, I, I, P, P],
+        "ems_moe_down": [P, P, I, P, P, I, I, I, P, P],
+        "ems_moe_combine": [P, P, P, I, I, I, I, P],
     }
     for name, args in sigs.items():
         fn = getattr(lib, name)
@@ -87,6 +99,10 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.ems_argmax_slices.restype = c_int
     lib.ems_paged_attention_scratch_bytes.argtypes = [I, I, I, I]
     lib.ems_paged_attention_scratch_bytes.restype = c_longlong
+    lib.ems_latent_attention_scratch_bytes.argtypes = [I, I, I, I]
+    lib.ems_latent_attention_scratch_bytes.restype = c_longlong
+    lib.ems_moe_tile_rows.argtypes = []
+    lib.ems_moe_tile_rows.restype = c_int
 
 
 _sm_counts: dict[int, int] = {}
@@ -250,6 +266,207 @@ def rope_kv_write(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim
         rotary_dim, _ptr(kcache, "kcache"), _ptr(vcache, "vcache"),
         _i32(block_tables, "block_tables"), bt_stride, page_size, 1 if write_kv else 0, _stream()),
         "rope_kv_write")
+
+
+def stream_inject(residual: torch.Tensor, tokens: torch.Tensor, embed: torch.Tensor | None,
+                  table: torch.Tensor | None, row: int = 0, deferred: torch.Tensor | None = None) -> None:
+    """residual[n, :] += embed[tokens[n], :] + table[row, :] in 32 bits (either may be None); a token
+    -(k + 1) reads deferred[k], as in `embedding`."""
+    n, h = residual.shape
+    assert residual.dtype == torch.float32 and (embed is not None or table is not None)
+    src = embed if embed is not None else table
+    assert embed is None or (embed.shape[1] == h and tokens.numel() >= n)
+    assert table is None or (table.shape[1] == h and 0 <= row < table.shape[0] and table.dtype == src.dtype)
+    vec = None if table is None else table[row]
+    _check(library().ems_stream_inject(_ptr(residual, "residual"), _i32(tokens, "tokens"),
+                                       None if deferred is None else _i32(deferred, "deferred"),
+                                       _ptr(embed, "embed"), _ptr(vec, "table row"), _dt(src), n, h, _stream()),
+           "stream_inject")
+
+
+def add_norm_grouped(delta: torch.Tensor | None, post_gain: torch.Tensor | None, post_groups: int, post_eps: float,
+                     residual: torch.Tensor, gain: torch.Tensor, groups: int, eps: float, out: torch.Tensor,
+                     rows: torch.Tensor | None = None) -> None:
+    """The grouped RMSNorm of the residual stream, with what joins the stream before it:
+
+        residual += delta                                   (post_gain None)
+        residual += grouped_norm(delta; post_groups, post_eps) * post_gain
+        out = grouped_norm(residual; groups, eps) * gain
+
+    where grouped_norm divides each of G equal consecutive parts of a row by sqrt(mean(part^2) + eps).
+    All 32-bit; only `out` is rounded.  With `rows` only those rows are computed, compactly, and
+    the residual is not written."""
+    h = residual.shape[-1]
+    assert residual.dtype == torch.float32 and gain.numel() == h and out.shape[-1] == h
+    n_out = residual.shape[0] if rows is None else rows.numel()
+    if delta is not None:
+        assert delta.dtype == out.dtype and delta.shape[-1] == h and (rows is not None or delta.shape[0] >= n_out)
+    if post_gain is not None:
+        assert delta is not None and post_gain.numel() == h and post_gain.dtype == gain.dtype
+    _check(library().ems_add_norm_grouped(
+        _ptr(delta, "delta"), _ptr(post_gain, "post_gain"), _dt(gain), int(post_groups), float(post_eps),
+        _ptr(residual, "residual"), _ptr(gain, "gain"), _dt(gain), int(groups), float(eps), _ptr(out, "out"),
+        _dt(out), _i32(rows, "rows"), n_out, h, 0 if rows is not None else 1, _stream()), "add_norm_grouped")
+
+
+GLU_ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2}
+
+
+def glu_act(gate_up: torch.Tensor, out: torch.Tensor, act: str) -> None:
+    """out[n, i] = act(gate_up[n, i]) * gate_up[n, I + i] for act in `GLU_ACTIVATIONS`."""
+    n, i = out.shape
+    assert gate_up.shape == (n, 2 * i) and gate_up.dtype == out.dtype
+    _check(library().ems_glu_act(_ptr(gate_up, "gate_up"), _ptr(out, "out"), _dt(out), n, i,
+                                 GLU_ACTIVATIONS[act], _stream()), "glu_act")
+
+
+def causal_taps(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor | None, slots: torch.Tensor | None,
+                cu_q: torch.Tensor, row_of_token: torch.Tensor, out: torch.Tensor, num_rows: int) -> None:
+    """out[t] = x[t] + sum_j weight[:, j] * x[t - taps + 1 + j] along each request's own tokens, with
+    the inputs before the step's first token taken from `state` ([slots, taps - 1, C] float32, the
+    last taps - 1 inputs of each request in time order), which is then brought up to date."""
+    n, c = x.shape
+    taps = weight.shape[1]
+    assert weight.shape[0] == c and out.shape == x.shape and out.dtype == x.dtype
+    if taps > 1:
+        assert state is not None and state.dtype == torch.float32 and state.shape[1:] == (taps - 1, c)
+        assert slots is not None
+    _check(library().ems_causal_taps(
+        _ptr(x, "x"), _ptr(weight, "weight"), _dt(weight), _ptr(state, "state"), _i32(slots, "slots"),
+        _i32(cu_q, "cu_q"), _i32(row_of_token, "row_of_token"), _ptr(out, "out"), _dt(out), n, num_rows, c, taps,
+        _stream()), "causal_taps", 2 if taps > 1 else 1)
+
+
+ROTARY_PAIRINGS = {"half": 0, "interleaved": 1}
+
+
+def latent_prep(proj: torch.Tensor, q_rank: int, kv_rank: int, rope_dim: int, q_gain: torch.Tensor,
+                kv_gain: torch.Tensor, eps: float, positions: torch.Tensor, row_of_token: torch.Tensor,
+                table: torch.Tensor | None, rot_dims: int, pairing: str, pages: torch.Tensor,
+                block_tables: torch.Tensor, cq: torch.Tensor, write: bool = True) -> None:
+    """The tokens of a step for latent attention.  proj: [N, >= q_rank + kv_rank + rope_dim] holds
+    [query latent | key/value latent | shared key part | ...] per row.  cq = RMSNorm(query latent)
+    * q_gain; the cache vector of the token, at its page slot, becomes [RMSNorm(kv latent) * kv_gain |
+    rotate(shared key part)].  pages: [num_pages, page_size, kv_rank + rope_dim]."""
+    n = proj.shape[0]
+    assert proj.stride(1) == 1 and proj.shape[1] >= q_rank + kv_rank + rope_dim
+    assert pages.dtype == proj.dtype == cq.dtype and pages.shape[2] == kv_rank + rope_dim
+    assert cq.shape == (n, q_rank) and q_gain.numel() == q_rank and kv_gain.numel() == kv_rank
+    assert q_gain.dtype == kv_gain.dtype and (table is None or table.dtype == torch.float32)
+    if not proj.is_cuda:
+        raise KernelError("proj must be a CUDA tensor (emberserve_b200 has no CPU path)")
+    _check(library().ems_latent_prep(
+        proj.data_ptr(), proj.stride(0), _dt(proj), n, q_rank, kv_rank, rope_dim, _ptr(q_gain, "q_gain"),
+        _ptr(kv_gain, "kv_gain"), _dt(q_gain), float(eps), _i32(positions, "positions"),
+        _i32(row_of_token, "row_of_token"), _ptr(table, "table"), rot_dims, ROTARY_PAIRINGS[pairing],
+        _ptr(pages, "pages"), _i32(block_tables, "block_tables"), block_tables.shape[1], pages.shape[1],
+        _ptr(cq, "cq"), 1 if write else 0, _stream()), "latent_prep")
+
+
+def rope_inplace(x: torch.Tensor, num_heads: int, head_stride: int, offset: int, rot_dims: int, pairing: str,
+                 positions: torch.Tensor, table: torch.Tensor) -> None:
+    """Rotate, in place, `rot_dims` numbers of every head of x[N, :] that start `offset` into the
+    head (head h begins at column h * head_stride), by the table rows of `positions`; pairing "half"
+    joins entry i with i + rot_dims/2, "interleaved" joins 2i with 2i + 1."""
+    assert x.stride(1) == 1 and table.dtype == torch.float32
+    _check(library().ems_rope_inplace(_ptr(x, "x"), _dt(x), x.shape[0], x.stride(0), head_stride, offset, num_heads,
+                                      rot_dims, ROTARY_PAIRINGS[pairing], _i32(positions, "positions"),
+                                      _ptr(table, "table"), _stream()), "rope_inplace")
+
+
+def latent_attention_scratch_bytes(num_tokens: int, num_heads: int, kv_rank: int, splits: int) -> int:
+    return int(library().ems_latent_attention_scratch_bytes(num_tokens, num_heads, kv_rank, splits))
+
+
+def latent_attention(qlat: torch.Tensor, q: torch.Tensor, rot_offset: int, head_stride: int, pages: torch.Tensor,
+                     block_tables: torch.Tensor, positions: torch.Tensor, row_of_token: torch.Tensor,
+                     out: torch.Tensor, num_heads: int, kv_rank: int, rope_dim: int, scale: float,
+                     splits: int = 1, scratch: torch.Tensor | None = None) -> None:
+    """Causal attention over cached latent vectors.  qlat: [H, N, kv_rank], the queries folded into
+    the latent space; q: [N, H * head_stride] whose `rope_dim` numbers from `rot_offset` on in every
+    head are the rotated query part; pages: [num_pages, page_size, kv_rank + rope_dim].
+    out[h, n, :] = sum_j softmax_j((qlat[h, n] . c_j + qrot[n, h] . krot_j) * scale) c_j over the
+    keys j <= position of token n of its request.  `splits` > 1 cuts every token's keys over
+    that many blocks (`scratch` takes the partial sums; a merge kernel follows)."""
+    h, n, r = qlat.shape
+    assert h == num_heads and r == kv_rank and out.shape == qlat.shape and pages.shape[2] == kv_rank + rope_dim
+    assert qlat.dtype == q.dtype == out.dtype == pages.dtype and q.stride(1) == 1
+    if not q.is_cuda:
+        raise KernelError("q must be a CUDA tensor (emberserve_b200 has no CPU path)")
+    _check(library().ems_latent_attention(
+        _ptr(qlat, "qlat"), q.data_ptr() + rot_offset * q.element_size(), q.stride(0), head_stride, _dt(q),
+        _ptr(pages, "pages"), _i32(block_tables, "block_tables"), block_tables.shape[1], pages.shape[1],
+        _i32(positions, "positions"), _i32(row_of_token, "row_of_token"), _ptr(out, "out"), n, num_heads, kv_rank,
+        rope_dim, float(scale), splits, _ptr(scratch, "scratch"),
+        0 if scratch is None else scratch.numel() * scratch.element_size(), _stream()),
+        "latent_attention", 2 if splits > 1 else 1)
+
+
+def heads_gate(ov: torch.Tensor, gate: torch.Tensor | None, out: torch.Tensor) -> None:
+    """out[n, h * V + i] = ov[h, n, i] * sigmoid(gate[n, h * V + i]); without a gate the plain
+    transposition.  `gate` may be a column range of a wider buffer."""
+    h, n, v = ov.shape
+    assert out.shape == (n, h * v) and out.dtype == ov.dtype
+    if gate is not None:
+        assert gate.shape == (n, h * v) and gate.stride(1) == 1 and gate.dtype == ov.dtype
+    _check(library().ems_heads_gate(_ptr(ov, "ov"), None if gate is None else gate.data_ptr(),
+                                    0 if gate is None else gate.stride(0), _ptr(out, "out"), _dt(out), n, h, v,
+                                    _stream()), "heads_gate")
+
+
+def moe_tile_rows() -> int:
+    """Rows of one tile of the grouped products of routed experts."""
+    return int(library().ems_moe_tile_rows())
+
+
+def moe_max_tiles(num_pairs: int, num_experts: int, tile_rows: int) -> int:
+    """The most tiles that `num_pairs` (token, choice) pairs spread over the experts can make."""
+    return num_pairs // tile_rows + min(num_experts, num_pairs)
+
+
+def moe_route(logits: torch.Tensor, top: int, renormalize: bool, ids: torch.Tensor, weights: torch.Tensor,
+              offsets: torch.Tensor, perm: torch.Tensor, plan: torch.Tensor, max_tiles: int) -> None:
+    """From router logits [N, E] (float32): softmax over all experts, the `top` largest per token
+    (ids, weights: [N, top]; the weights are the scores, divided by their sum if `renormalize`),
+    the first sorted row of every expert (offsets [E + 1]), the pairs t * top + k in expert order
+    (perm [N * top]) and the tiles of the grouped products (plan: count, then expert / first row /
+    rows per tile)."""
+    n, e = logits.shape
+    assert logits.dtype == torch.float32 and weights.dtype == torch.float32
+    assert ids.numel() >= n * top and weights.numel() >= n * top and perm.numel() >= n * top
+    assert offsets.numel() >= e + 1 and plan.numel() >= 1 + 3 * max_tiles
+    _check(library().ems_moe_route(_ptr(logits, "logits"), n, e, top, 1 if renormalize else 0, _i32(ids, "ids"),
+                                   _ptr(weights, "weights"), _i32(offsets, "offsets"), _i32(perm, "perm"),
+                                   _i32(plan, "plan"), max_tiles, _stream()), "moe_route")
+
+
+def moe_up(x: torch.Tensor, wgu: torch.Tensor, perm: torch.Tensor, offsets: torch.Tensor, plan: torch.Tensor,
+           max_tiles: int, top: int, act: str, out: torch.Tensor) -> None:
+    """out[i, :] = act(x[t] Wg[e]^T) * (x[t] Wu[e]^T) for sorted pair i (token t = perm[i] // top) of
+    expert e; wgu: [E, 2 * ff, K] with the gate rows first."""
+    e, ff2, k = wgu.shape
+    assert x.shape[1] == k and out.shape[1] * 2 == ff2 and x.dtype == wgu.dtype == out.dtype
+    _check(library().ems_moe_up(_ptr(x, "x"), _ptr(wgu, "wgu"), _dt(x), _i32(perm, "perm"), _i32(plan, "plan"),
+                                max_tiles, top, ff2 // 2, k, GLU_ACTIVATIONS[act], _ptr(out, "out"), _stream()),
+           "moe_up")
+
+
+def moe_down(act: torch.Tensor, wdown: torch.Tensor, perm: torch.Tensor, offsets: torch.Tensor, plan: torch.Tensor,
+             max_tiles: int, y: torch.Tensor) -> None:
+    """y[perm[i], :] = act[i, :] Wd[e]^T (float32, in pair order) for sorted pair i of expert e;
+    wdown: [E, H, ff]."""
+    e, h, ff = wdown.shape
+    assert act.shape[1] == ff and y.shape[1] == h and y.dtype == torch.float32 and act.dtype == wdown.dtype
+    _check(library().ems_moe_down(_ptr(act, "act"), _ptr(wdown, "wdown"), _dt(act), _i32(perm, "perm"),
+                                  _i32(plan, "plan"), max_tiles, h, ff, _ptr(y, "y"), _stream()), "moe_down")
+
+
+def moe_combine(y: torch.Tensor, weights: torch.Tensor, out: torch.Tensor, top: int) -> None:
+    """out[t, :] = sum_k weights[t, k] * y[t * top + k, :], k ascending."""
+    n, h = out.shape
+    assert y.dtype == torch.float32 and weights.dtype == torch.float32 and y.shape[1] == h
+    _check(library().ems_moe_combine(_ptr(y, "y"), _ptr(weights, "weights"), _ptr(out, "out"), _dt(out), n, top, h,
+                                     _stream()), "moe_combine")
 
 
 def attention_scratch_bytes(num_tokens: int, num_heads: int, head_dim: int, splits: int) -> int:

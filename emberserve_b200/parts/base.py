@@ -63,6 +63,26 @@ class PagedKV:
     head_dim: int
     window: int | None = None
 
+    paged = True
+
+    def elements_per_token(self) -> int:
+        return 2 * self.num_kv_heads * self.head_dim
+
+
+@dataclass(frozen=True)
+class PagedLatent:
+    """ONE vector of `dim` numbers per token, in pages: what a latent-attention mixer keeps (the
+    compressed key/value latent and the rotated key part that all heads share, side by side).
+    `window` as for PagedKV."""
+
+    dim: int
+    window: int | None = None
+
+    paged = True
+
+    def elements_per_token(self) -> int:
+        return self.dim
+
 
 @dataclass(frozen=True)
 class FixedState:
@@ -71,8 +91,10 @@ class FixedState:
     shape: tuple[int, ...]
     dtype: str = "float32"
 
+    paged = False
 
-CacheNeed = PagedKV | FixedState
+
+CacheNeed = PagedKV | PagedLatent | FixedState
 
 
 @dataclass
@@ -85,6 +107,17 @@ class PagedKVHandle:
     page_size: int
     window: int | None
     write: bool  # False: read what another layer call wrote in this step
+
+
+@dataclass
+class PagedLatentHandle:
+    """One cache entry of kind PagedLatent as a mixer sees it during a step."""
+
+    pages: torch.Tensor  # [num_pages, page_size, dim]
+    block_tables: torch.Tensor  # [rows, max_pages] int32, page ids of this entry's group
+    page_size: int
+    window: int | None
+    write: bool
 
 
 @dataclass
@@ -145,6 +178,25 @@ class NormRequest:
     residual: torch.Tensor  # [num_tokens, width] float32, updated in place
     gain: torch.Tensor  # [width]
     eps: float
+
+
+@dataclass
+class NormedDelta:
+    """A sub-layer's output that has to pass a norm of its OWN before it joins the residual stream
+    (a block with a norm behind each sub-layer as well as before it).  The norm that receives it
+    (`Norm.forward`) applies `norm` to `x`, adds the result into the 32-bit residual and goes on
+    with its own work, in one kernel; nothing of the intermediate is rounded."""
+
+    x: torch.Tensor  # [num_tokens, width], activation dtype
+    norm: "Norm"
+
+    @property
+    def shape(self):
+        return self.x.shape
+
+    @property
+    def dtype(self):
+        return self.x.dtype
 
 
 @dataclass
@@ -294,7 +346,10 @@ class Block(Part):
     (delta, residual): `delta` is the previous sub-layer's output that has not been
     added to the 32-bit residual stream yet (None right after the embedding)."""
 
-    def cache_need(self) -> CacheNeed | None:
+    def cache_need(self) -> "CacheNeed | tuple[CacheNeed, ...] | None":
+        """What one call of the block keeps between steps: one need, or a tuple of needs (pages of
+        a mixer beside the fixed-size state of a convolution, say); `forward` is then handed a
+        tuple of handles in the same order, and the layer call names a tuple of cache entries."""
         raise NotImplementedError
 
     def entry_norm(self) -> "Norm | None":
@@ -312,13 +367,13 @@ class Block(Part):
 # ---------------------------------------------------------------------------------------
 # registries: spec kind -> part class
 
-_CATEGORIES = ("mixer", "feed_forward", "norm", "position", "block")
+_CATEGORIES = ("mixer", "feed_forward", "norm", "position", "block", "conv")
 _REGISTRY: dict[str, dict[str, type[Part]]] = {c: {} for c in _CATEGORIES}
 
 
 def register_part(category: str, kind: str, cls: type[Part] | None = None):
     """Register `cls` as the part built for specs of `kind` in `category` (one of
-    mixer, feed_forward, norm, position, block).  Usable as a decorator."""
+    mixer, feed_forward, norm, position, block, conv).  Usable as a decorator."""
     if category not in _REGISTRY:
         raise KeyError(f"unknown part category {category!r}; one of {_CATEGORIES}")
 

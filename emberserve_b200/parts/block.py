@@ -1,4 +1,8 @@
-"""Pre-norm residual block: ``h += mixer(norm1(h)); h += ffn(norm2(h))``.
+"""Residual blocks.
+
+Pre-norm: ``h += mixer(norm1(h)); h += ffn(norm2(h))``.
+Sandwich (a norm before AND behind every sub-layer, optionally a short convolution before the
+mixer, optionally no feed-forward): ``h += norm1b(mixer(conv(norm1(h)))); h += norm2b(ffn(norm2(h)))``.
 
 Written on the pair (delta, residual) so that each norm performs the add that precedes
 it (``emberserve/model/qwen2.py:122-164``): the block receives the previous block's
@@ -12,7 +16,7 @@ from typing import Any
 
 import torch
 
-from emberserve_b200.parts.base import (Block, CacheNeed, Part, StepContext, build_part,
+from emberserve_b200.parts.base import (Block, CacheNeed, NormedDelta, Part, StepContext, build_part,
                                         register_part)
 
 
@@ -59,3 +63,69 @@ class PreNormBlock(Block):
         out = self.ffn.forward(y, ctx)
         ctx.extra["norm_behind"] = None
         return out
+
+
+@dataclass(frozen=True)
+class SandwichBlockSpec:
+    mixer: Any
+    mixer_norm: Any
+    mixer_post_norm: Any
+    feed_forward: Any | None = None  # None: the block is its mixer alone
+    ffn_norm: Any | None = None
+    ffn_post_norm: Any | None = None
+    mixer_conv: Any | None = None  # spec of a "conv" part that filters what the mixer reads
+    kind: str = "sandwich"
+
+
+@register_part("block", "sandwich")
+class SandwichBlock(Block):
+    """A sub-layer's output passes a norm of its own before it joins the stream.  That norm, the
+    32-bit add and the norm in front of the NEXT sub-layer are one kernel: the block hands its
+    output on as a `NormedDelta`, and the norm that receives it does all three.  What the block
+    keeps between steps is the mixer's cache entry and, with a convolution, its state: two entries
+    per layer call."""
+
+    def __init__(self, spec: SandwichBlockSpec, prefix: str, shared=None) -> None:
+        super().__init__(spec, prefix, shared)
+        self.mixer_norm = build_part("norm", spec.mixer_norm, prefix + ".mixer_norm", self.shared)
+        self.mixer = build_part("mixer", spec.mixer, prefix + ".mixer", self.shared)
+        self.mixer_post_norm = build_part("norm", spec.mixer_post_norm, prefix + ".mixer_post_norm", self.shared)
+        self.conv = (build_part("conv", spec.mixer_conv, prefix + ".mixer_conv", self.shared)
+                     if spec.mixer_conv is not None else None)
+        self.ffn = self.ffn_norm = self.ffn_post_norm = None
+        if spec.feed_forward is not None:
+            if spec.ffn_norm is None or spec.ffn_post_norm is None:
+                raise ValueError(f"{prefix}: a feed-forward needs its two norms")
+            self.ffn_norm = build_part("norm", spec.ffn_norm, prefix + ".ffn_norm", self.shared)
+            self.ffn = build_part("feed_forward", spec.feed_forward, prefix + ".ffn", self.shared)
+            self.ffn_post_norm = build_part("norm", spec.ffn_post_norm, prefix + ".ffn_post_norm", self.shared)
+        self._conv_state = self.conv is not None and self.conv.cache_need() is not None
+
+    def children(self) -> dict[str, Part]:
+        out = {"mixer_norm": self.mixer_norm, "mixer": self.mixer, "mixer_post_norm": self.mixer_post_norm}
+        if self.conv is not None:
+            out["mixer_conv"] = self.conv
+        if self.ffn is not None:
+            out.update(ffn_norm=self.ffn_norm, ffn=self.ffn, ffn_post_norm=self.ffn_post_norm)
+        return out
+
+    def cache_need(self):
+        need = self.mixer.cache_need()
+        if not self._conv_state:
+            return need
+        state = self.conv.cache_need()
+        return (need, state) if need is not None else state
+
+    def forward(self, delta, residual: torch.Tensor, ctx: StepContext, cache: Any):
+        ctx.extra.pop("next_norm", None)
+        mixer_cache, conv_cache = cache, None
+        if self._conv_state:
+            mixer_cache, conv_cache = cache if isinstance(cache, tuple) else (None, cache)
+        x = self.mixer_norm.forward(delta, residual, ctx)
+        if self.conv is not None:
+            x = self.conv.forward(x, ctx, conv_cache)
+        a = NormedDelta(self.mixer.forward(x, ctx, mixer_cache), self.mixer_post_norm)
+        if self.ffn is None:
+            return a
+        y = self.ffn_norm.forward(a, residual, ctx)
+        return NormedDelta(self.ffn.forward(y, ctx), self.ffn_post_norm)

@@ -24,10 +24,25 @@ from emberserve_b200.parts.linear import linear_f32_out
 
 
 @dataclass(frozen=True)
+class StreamInject:
+    """What is added to the residual stream right before a layer call runs (32-bit sums): the
+    embedding of the step's tokens once more, and / or one row of a table of vectors that the
+    decoder owns (``DecoderSpec.tables``).  A decoder that runs some of its layers several times
+    marks the beginning of each pass this way."""
+
+    embedding: bool = False
+    table: str | None = None  # key of DecoderSpec.tables
+    row: int = 0
+
+
+@dataclass(frozen=True)
 class LayerCall:
     layer: int  # index into DecoderSpec.layers
-    cache: int | None  # id of the cache entry this call uses; None = the block keeps nothing
+    # id of the cache entry this call uses (a tuple of ids for a block that keeps several
+    # things, in the order of its `cache_need()`); None = the block keeps nothing
+    cache: "int | tuple[int, ...] | None"
     write: bool = True  # False: the call reads the entry another call wrote in this step
+    inject: StreamInject | None = None
 
 
 @dataclass
@@ -44,6 +59,9 @@ class DecoderSpec:
     # suffixes (``emberserve/model/weights.py:22`` skips rotary_emb.inv_freq).
     ignorable: tuple[str, ...] = ("rotary_emb.inv_freq",)
     embedding_position: Any | None = None
+    # Tables of vectors that belong to the decoder itself: local name -> (checkpoint tensor, rows);
+    # each is [rows, hidden].  `StreamInject` names them.
+    tables: dict[str, tuple[str, int]] = field(default_factory=dict)
 
 
 class Decoder:
@@ -57,6 +75,7 @@ class Decoder:
                                if spec.embedding_position is not None else None)
         self.embed: torch.Tensor | None = None
         self.head: torch.Tensor | None = None
+        self.tables: dict[str, torch.Tensor] = {}
         self._entries = self._check_order()
 
     # ---- structure -------------------------------------------------------------------
@@ -67,22 +86,32 @@ class Decoder:
             if not 0 <= call.layer < len(self.blocks):
                 raise ValueError(f"order[{pos}] names layer {call.layer}, model has {len(self.blocks)}")
             need = self.blocks[call.layer].cache_need()
+            if call.inject is not None and call.inject.table is not None:
+                rows = spec.tables.get(call.inject.table, (None, 0))[1]
+                if not 0 <= call.inject.row < rows:
+                    raise ValueError(f"order[{pos}]: row {call.inject.row} of table {call.inject.table!r} "
+                                     f"({rows} rows)")
             if call.cache is None:
                 if need is not None:
                     raise ValueError(f"order[{pos}]: layer {call.layer} needs a cache entry")
                 continue
             if need is None:
                 raise ValueError(f"order[{pos}]: layer {call.layer} keeps nothing but names entry {call.cache}")
-            if call.write:
-                if call.cache in entries:
-                    raise ValueError(f"order[{pos}]: cache entry {call.cache} is written twice")
-                entries[call.cache] = need
-            else:
-                if call.cache not in entries:
-                    raise ValueError(f"order[{pos}]: reads cache entry {call.cache} before it is written")
-                if entries[call.cache] != need:
-                    raise ValueError(f"order[{pos}]: layer {call.layer} needs {need}, entry "
-                                     f"{call.cache} holds {entries[call.cache]}")
+            if isinstance(need, tuple) != isinstance(call.cache, tuple) or (
+                    isinstance(need, tuple) and len(need) != len(call.cache)):
+                raise ValueError(f"order[{pos}]: layer {call.layer} needs {need}, the call names {call.cache}")
+            pairs = list(zip(call.cache, need)) if isinstance(need, tuple) else [(call.cache, need)]
+            for entry, one in pairs:
+                if call.write:
+                    if entry in entries:
+                        raise ValueError(f"order[{pos}]: cache entry {entry} is written twice")
+                    entries[entry] = one
+                else:
+                    if entry not in entries:
+                        raise ValueError(f"order[{pos}]: reads cache entry {entry} before it is written")
+                    if entries[entry] != one:
+                        raise ValueError(f"order[{pos}]: layer {call.layer} needs {one}, entry "
+                                         f"{entry} holds {entries[entry]}")
         if sorted(entries) != list(range(len(entries))):
             raise ValueError(f"cache entry ids must be 0..n-1, got {sorted(entries)}")
         return [entries[i] for i in range(len(entries))]
@@ -113,6 +142,8 @@ class Decoder:
             "embed": ParamSpec((s.vocab_size, s.hidden), [Source(s.embed_name)])}
         if s.head_name is not None:
             table["head"] = ParamSpec((s.vocab_size, s.hidden), [Source(s.head_name)])
+        for local, (name, rows) in s.tables.items():
+            table[f"table.{local}"] = ParamSpec((rows, s.hidden), [Source(name)])
         for path, part in self._walk():
             for local, ps in part.param_specs().items():
                 table[f"{path}.{local}"] = ps
@@ -146,6 +177,7 @@ class Decoder:
     def bind(self, params: dict[str, torch.Tensor]) -> None:
         self.embed = params["embed"]
         self.head = params.get("head", self.embed)  # tied: one tensor serves both
+        self.tables = {local: params[f"table.{local}"] for local in self.spec.tables}
         for path, part in self._walk():
             mine = {local: params[f"{path}.{local}"] for local in part.param_specs()}
             if mine:
@@ -155,6 +187,8 @@ class Decoder:
         out = {"embed": self.embed}
         if self.spec.head_name is not None:
             out["head"] = self.head
+        for local in self.spec.tables:
+            out[f"table.{local}"] = self.tables[local]
         for path, part in self._walk():
             for local in part.param_specs():
                 out[f"{path}.{local}"] = getattr(part, local)
@@ -178,7 +212,15 @@ class Decoder:
             # last product (`Block.entry_norm`); the final norm is always a kernel of its own
             ctx.extra["next_norm"] = (self.blocks[s.order[i + 1].layer].entry_norm()
                                       if i + 1 < len(s.order) else None)
+            if call.inject is not None:
+                # (sums commute: a delta that has not joined the stream yet may follow)
+                inj = call.inject
+                K.stream_inject(residual, ctx.tokens, self.embed if inj.embedding else None,
+                                self.tables[inj.table] if inj.table is not None else None, inj.row,
+                                deferred=ctx.deferred)
             delta = self.blocks[call.layer].forward(delta, residual, ctx, handle)
+            if "layer_probe" in ctx.extra:  # a debugging aid: look at the stream after every layer call
+                ctx.extra["layer_probe"](i, delta, residual)
         logits = ctx.scratch("logits", (num_want, s.vocab_size), torch.float32)
         if num_want == 0:
             # still fold the last delta in?  Nothing reads the residual after the step.

@@ -1,4 +1,5 @@
-"""Dense gated feed-forward (SwiGLU): ``down(silu(gate(x)) * up(x))``, no biases.
+"""Dense gated feed-forward: ``down(act(gate(x)) * up(x))``, no biases; act is SiLU (SwiGLU)
+unless the spec names another (``relu``, ``gelu_tanh``), which takes the unfused kernels.
 
 gate and up are one fused projection whose first I output columns are the gate and the
 last I the up part (``emberserve/model/qwen2.py:48-61``); the activation is
@@ -25,6 +26,8 @@ class SwiGLUSpec:
     up_name: str
     down_name: str
     kind: str = "swiglu"
+    activation: str = "silu"  # one of kernels.GLU_ACTIVATIONS
+    weight_suffix: str = ".weight"  # what follows the three names in the checkpoint
 
 
 @register_part("feed_forward", "swiglu")
@@ -33,13 +36,18 @@ class SwiGLU(FeedForward):
     wgu: torch.Tensor
     wdown: torch.Tensor
 
+    def __init__(self, spec: SwiGLUSpec, prefix: str, shared=None) -> None:
+        super().__init__(spec, prefix, shared)
+        if spec.activation not in K.GLU_ACTIVATIONS:
+            raise ValueError(f"activation {spec.activation!r}: one of {sorted(K.GLU_ACTIVATIONS)}")
+
     def param_specs(self) -> dict[str, ParamSpec]:
         s: SwiGLUSpec = self.spec
         i = s.intermediate
         return {
-            "wgu": ParamSpec((2 * i, s.hidden), [Source(s.gate_name + ".weight", (0, i)),
-                                                 Source(s.up_name + ".weight", (i, 2 * i))]),
-            "wdown": ParamSpec((s.hidden, i), [Source(s.down_name + ".weight")]),
+            "wgu": ParamSpec((2 * i, s.hidden), [Source(s.gate_name + s.weight_suffix, (0, i)),
+                                                 Source(s.up_name + s.weight_suffix, (i, 2 * i))]),
+            "wdown": ParamSpec((s.hidden, i), [Source(s.down_name + s.weight_suffix)]),
         }
 
     def streamed_params(self) -> list[str]:
@@ -53,7 +61,11 @@ class SwiGLU(FeedForward):
         s: SwiGLUSpec = self.spec
         n = x.shape[0]
         act = ctx.scratch("ffn_act", (n, s.intermediate), ctx.dtype)
-        if not gated_linear(x, self.wgu, act):  # both projections and SiLU in one kernel, where one takes the sizes
+        if s.activation != "silu":  # the kernels with the activation in their epilogue know SiLU only
+            gu = ctx.scratch("gate_up", (n, 2 * s.intermediate), ctx.dtype)
+            linear(x, self.wgu, None, gu, ctx.scratch)
+            K.glu_act(gu, act, s.activation)
+        elif not gated_linear(x, self.wgu, act):  # both projections and SiLU in one kernel, where one takes the sizes
             gu = ctx.scratch("gate_up", (n, 2 * s.intermediate), ctx.dtype)
             linear(x, self.wgu, None, gu, ctx.scratch)
             K.silu_mul(gu, act)

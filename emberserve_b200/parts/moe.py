@@ -1,0 +1,103 @@
+"""Routed experts: a feed-forward made of `num_experts` small gated feed-forwards, of which
+every token uses `top_k`.
+
+    z = Wr h                       router logits, 32-bit
+    s = softmax(z)                 over ALL experts
+    chosen = the top_k largest s   (ties: the lower index)
+    weight = s[chosen]             as they are, or divided by their sum with `renormalize`
+    y = sum_k weight_k * Wd[e_k] (act(Wg[e_k] h) * (Wu[e_k] h))
+
+The (token, choice) pairs are sorted by expert on the device and the experts run as two grouped
+matrix products over the sorted rows (``csrc/moe_routed.cu``); nothing is read back to the host,
+so the step can be captured in a CUDA graph.  A token's result is computed row by row and summed
+over its choices in a fixed order: it does not depend on what else is in the step.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from emberserve_b200 import kernels as K
+from emberserve_b200.parts.base import FeedForward, ParamSpec, Source, StepContext, register_part
+
+
+@dataclass(frozen=True)
+class RoutedGLUSpec:
+    hidden: int
+    intermediate: int  # of one expert
+    num_experts: int
+    top_k: int
+    router_name: str  # checkpoint tensor [num_experts, hidden]
+    # per expert, the checkpoint tensors of its gate, up and down projections
+    expert_names: tuple[tuple[str, str, str], ...]
+    activation: str = "silu"
+    renormalize: bool = False
+    kind: str = "routed_glu"
+
+
+@register_part("feed_forward", "routed_glu")
+class RoutedGLU(FeedForward):
+    router: torch.Tensor
+    wgu: torch.Tensor  # [E * 2 ff, hidden]: per expert the gate rows, then the up rows
+    wdown: torch.Tensor  # [E * hidden, ff]
+
+    def __init__(self, spec: RoutedGLUSpec, prefix: str, shared=None) -> None:
+        super().__init__(spec, prefix, shared)
+        if not 1 <= spec.top_k <= spec.num_experts:
+            raise ValueError(f"top_k={spec.top_k} of {spec.num_experts} experts")
+        if len(spec.expert_names) != spec.num_experts:
+            raise ValueError("one (gate, up, down) name triple per expert is needed")
+        if spec.activation not in K.GLU_ACTIVATIONS:
+            raise ValueError(f"activation {spec.activation!r}: one of {sorted(K.GLU_ACTIVATIONS)}")
+        self._router32: torch.Tensor | None = None
+
+    def param_specs(self) -> dict[str, ParamSpec]:
+        s: RoutedGLUSpec = self.spec
+        ff, hid = s.intermediate, s.hidden
+        gu, down = [], []
+        for e, (g, u, d) in enumerate(s.expert_names):
+            gu += [Source(g, (2 * e * ff, (2 * e + 1) * ff)), Source(u, ((2 * e + 1) * ff, (2 * e + 2) * ff))]
+            down.append(Source(d, (e * hid, (e + 1) * hid)))
+        return {
+            "router": ParamSpec((s.num_experts, hid), [Source(s.router_name)]),
+            "wgu": ParamSpec((s.num_experts * 2 * ff, hid), gu),
+            "wdown": ParamSpec((s.num_experts * hid, ff), down),
+        }
+
+    def bind(self, params: dict[str, torch.Tensor]) -> None:
+        super().bind(params)
+        self._router32 = self.router.float()  # the logits are a 32-bit product
+
+    def scratch_elements_per_token(self) -> int:
+        s: RoutedGLUSpec = self.spec
+        # activations of the chosen experts, their 32-bit outputs (two elements each), the result
+        return s.top_k * (s.intermediate + 2 * s.hidden) + 3 * s.hidden
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        s: RoutedGLUSpec = self.spec
+        n, e, top = x.shape[0], s.num_experts, s.top_k
+        pairs = n * top
+        x32 = x
+        if x.dtype != torch.float32:
+            x32 = ctx.scratch("moe_x32", (n, s.hidden), torch.float32)
+            x32.copy_(x)
+        logits = ctx.scratch("moe_logits", (n, e), torch.float32)
+        torch.mm(x32, self._router32.t(), out=logits)
+        tile = K.moe_tile_rows()
+        max_tiles = K.moe_max_tiles(pairs, e, tile)
+        ids = ctx.scratch("moe_ids", (pairs,), torch.int32)
+        weights = ctx.scratch("moe_weights", (pairs,), torch.float32)
+        offsets = ctx.scratch("moe_offsets", (e + 1,), torch.int32)
+        perm = ctx.scratch("moe_perm", (pairs,), torch.int32)
+        plan = ctx.scratch("moe_plan", (1 + 3 * max_tiles,), torch.int32)
+        K.moe_route(logits, top, s.renormalize, ids, weights, offsets, perm, plan, max_tiles)
+        act = ctx.scratch("moe_act", (pairs, s.intermediate), ctx.dtype)
+        K.moe_up(x, self.wgu.view(e, 2 * s.intermediate, s.hidden), perm, offsets, plan, max_tiles, top,
+                 s.activation, act)
+        y = ctx.scratch("moe_y", (pairs, s.hidden), torch.float32)
+        K.moe_down(act, self.wdown.view(e, s.hidden, s.intermediate), perm, offsets, plan, max_tiles, y)
+        out = ctx.scratch("ffn_out", (n, s.hidden), ctx.dtype)
+        K.moe_combine(y, weights, out, top)
+        return out

@@ -13,8 +13,8 @@ from dataclasses import dataclass
 import torch
 
 from emberserve_b200 import kernels as K
-from emberserve_b200.parts.base import (Norm, NormRequest, ParamSpec, ScaledRows, Source, StepContext,
-                                        register_part)
+from emberserve_b200.parts.base import (Norm, NormedDelta, NormRequest, ParamSpec, ScaledRows, Source,
+                                        StepContext, register_part)
 
 
 # EMBERSERVE_SPLIT_NORMS=0 keeps the norm a kernel of its own in every step (for comparisons).
@@ -59,4 +59,52 @@ class RMSNorm(Norm):
         n = residual.shape[0] if rows is None else rows.numel()
         out = ctx.scratch("normed" if rows is None else "normed_rows", (n, s.dim), ctx.dtype)
         K.add_rmsnorm(delta, residual, self.weight, out, s.eps, rows=rows)
+        return out
+
+
+@dataclass(frozen=True)
+class GroupedRMSNormSpec:
+    dim: int
+    groups: int  # the width is cut into this many equal consecutive parts, each with its own statistics
+    eps: float
+    weight_name: str  # checkpoint tensor of the gain, [dim]
+    kind: str = "rmsnorm_grouped"
+
+
+@register_part("norm", "rmsnorm_grouped")
+class GroupedRMSNorm(Norm):
+    """RMSNorm in groups: ``y[g] = x[g] / sqrt(mean(x[g]^2) + eps)`` for each of `groups` equal
+    consecutive parts g of the vector, then ``y * weight`` over the whole (groups = 1 is the plain
+    RMSNorm, with the gain applied to the unrounded 32-bit value).  All of it in 32 bits.
+
+    `forward` takes three kinds of `delta`: None, a tensor (added to the stream as it is), or a
+    `NormedDelta` whose own norm is a GroupedRMSNorm: then ``residual += thatnorm(delta.x)`` and
+    this norm of the new residual are one kernel."""
+
+    weight: torch.Tensor
+
+    def __init__(self, spec: GroupedRMSNormSpec, prefix: str, shared=None) -> None:
+        super().__init__(spec, prefix, shared)
+        if spec.groups <= 0 or spec.dim % spec.groups:
+            raise ValueError(f"a norm over {spec.dim} numbers cannot have {spec.groups} equal groups")
+
+    def param_specs(self) -> dict[str, ParamSpec]:
+        s: GroupedRMSNormSpec = self.spec
+        return {"weight": ParamSpec((s.dim,), [Source(s.weight_name)], init="ones")}
+
+    def scratch_elements_per_token(self) -> int:
+        return self.spec.dim
+
+    def forward(self, delta, residual: torch.Tensor, ctx: StepContext,
+                rows: torch.Tensor | None = None) -> torch.Tensor:
+        s: GroupedRMSNormSpec = self.spec
+        n = residual.shape[0] if rows is None else rows.numel()
+        out = ctx.scratch("normed" if rows is None else "normed_rows", (n, s.dim), ctx.dtype)
+        x, gain, groups, eps = delta, None, 1, 0.0
+        if isinstance(delta, NormedDelta):
+            post = delta.norm
+            if not isinstance(post, GroupedRMSNorm):
+                raise TypeError(f"{self.prefix}: a delta normed by {type(post).__name__} cannot be taken")
+            x, gain, groups, eps = delta.x, post.weight, post.spec.groups, post.spec.eps
+        K.add_norm_grouped(x, gain, groups, eps, residual, self.weight, s.groups, s.eps, out, rows=rows)
         return out

@@ -1,5 +1,6 @@
-"""Rotary position encoding, rotate-half ("NeoX") pairing: dimension i of a head pairs
-with dimension i + rotary_dim/2.
+"""Rotary position encoding.  Two pairings share one table: rotate-half ("NeoX"), where
+dimension i of a head pairs with dimension i + rotary_dim/2, and interleaved, where dimension
+2i pairs with 2i + 1 (``RotaryInterleaved``; a mixer reads the pairing from ``part.pairing``).
 
 ``inv_freq[i] = 1 / theta^(2i / rotary_dim)`` and ``angle = pos * inv_freq[i]``, both in
 float32, as ``emberserve/model/rope.py:68-82`` computes them; the table of (cos, sin) is
@@ -33,6 +34,8 @@ def inv_frequencies(rotary_dim: int, theta: float) -> torch.Tensor:
 
 @register_part("position", "rotary_neox")
 class RotaryNeox(PositionEncoding):
+    pairing = "half"
+
     def __init__(self, spec: RotarySpec, prefix: str, shared=None) -> None:
         super().__init__(spec, prefix, shared)
         if spec.rotary_dim % 2 or spec.rotary_dim <= 0:
@@ -49,3 +52,19 @@ class RotaryNeox(PositionEncoding):
             inv = inv_frequencies(s.rotary_dim, s.theta).to(device)
             self._table = K.rope_table(inv, s.max_positions)
         return self._table, s.rotary_dim
+
+
+@dataclass(frozen=True)
+class RotaryInterleavedSpec:
+    rotary_dim: int
+    theta: float
+    max_positions: int
+    kind: str = "rotary_interleaved"
+
+
+@register_part("position", "rotary_interleaved")
+class RotaryInterleaved(RotaryNeox):
+    """The same angles (``pos * theta^(-2i/rotary_dim)``) and the same table; the pair that angle i
+    turns is (2i, 2i + 1)."""
+
+    pairing = "interleaved"

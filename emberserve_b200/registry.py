@@ -1,7 +1,8 @@
 """One registry from an architecture's name to its typed config and its builder.
 
 The name is the first entry of ``architectures`` in ``config.json``
-(``"Qwen2ForCausalLM"``); a checkpoint without that key is matched by ``model_type``.
+(``"Qwen2ForCausalLM"``) or the string under ``architecture``; a checkpoint without either key
+is matched by ``model_type``.
 The builder turns the typed config into a ``DecoderSpec``: which parts, with which
 sizes, in which order, reading which checkpoint tensors.  Adding an architecture is one
 ``register_architecture`` call; nothing else in the package names a model.
@@ -46,7 +47,9 @@ def registered_architectures() -> list[str]:
 def resolve_architecture(cfg: dict[str, Any]) -> Architecture:
     """The architecture that serves a ``config.json`` dict."""
     _ensure_builtin()
-    names = cfg.get("architectures") or []
+    names = list(cfg.get("architectures") or [])
+    if isinstance(cfg.get("architecture"), str):
+        names.append(cfg["architecture"])
     for name in names:
         if name in _ARCHITECTURES:
             return _ARCHITECTURES[name]

@@ -214,8 +214,206 @@ def check_status(clear=True):
     return None
 
 
+# ---- the residual stream of decoders with a norm on both sides of every sub-layer ----------
+
+def stream_inject(residual, tokens, embed, table, row=0, deferred=None):
+    n = residual.shape[0]
+    if embed is not None:
+        tok = tokens[:n].long()
+        if deferred is not None and bool((tok < 0).any()):
+            tok = torch.where(tok < 0, deferred.long()[(-(tok + 1)).clamp(min=0)], tok)
+        residual += embed[tok].float()
+    if table is not None:
+        residual += table[row].float()
+
+
+def _group_norm(x, groups, eps):
+    n, h = x.shape
+    parts = x.view(n, groups, h // groups)
+    return (parts / torch.sqrt(parts.pow(2).mean(-1, keepdim=True) + eps)).reshape(n, h)
+
+
+def add_norm_grouped(delta, post_gain, post_groups, post_eps, residual, gain, groups, eps, out, rows=None):
+    idx = None if rows is None else rows.long()
+    r = residual if idx is None else residual[idx]
+    if delta is not None:
+        d = (delta[:residual.shape[0]] if idx is None else delta[idx]).float()
+        if post_gain is not None:
+            d = _group_norm(d, post_groups, post_eps) * post_gain.float()
+        r = r + d
+        if idx is None:
+            residual.copy_(r)
+    out[:r.shape[0]].copy_((_group_norm(r, groups, eps) * gain.float()).to(out.dtype))
+
+
+def _glu_activation(g, act):
+    if act == "relu":
+        return torch.relu(g)
+    if act == "gelu_tanh":
+        return 0.5 * g * (1 + torch.tanh(math.sqrt(2 / math.pi) * (g + 0.044715 * g ** 3)))
+    return g / (1 + torch.exp(-g))
+
+
+def glu_act(gate_up, out, act):
+    i = out.shape[1]
+    g, u = gate_up[:, :i].float(), gate_up[:, i:].float()
+    out.copy_((_glu_activation(g, act) * u).to(out.dtype))
+
+
+def causal_taps(x, weight, state, slots, cu_q, row_of_token, out, num_rows):
+    taps = weight.shape[1]
+    cu = cu_q.tolist()
+    w = weight.float()
+    for b in range(num_rows):
+        q0, q1 = cu[b], cu[b + 1]
+        if q1 <= q0:
+            continue
+        h = x[q0:q1].float()
+        if taps > 1:
+            slot = int(slots[b])
+            full = torch.cat((state[slot], h), 0)
+        else:
+            full = h
+        conv = torch.zeros_like(h)
+        for j in range(taps):
+            conv += w[:, j] * full[j:j + h.shape[0]]
+        out[q0:q1] = (h + conv).to(out.dtype)
+        if taps > 1:
+            state[slot] = full[-(taps - 1):]
+
+
+def _rotate_pairs(v, cs, dims, pairing):
+    """v: [..., >= dims] float; cs: [..., dims/2, 2] broadcastable."""
+    half = dims // 2
+    c, s = cs[..., 0], cs[..., 1]
+    out = v.clone()
+    if pairing == "half":
+        a, b = v[..., :half], v[..., half:dims]
+        out[..., :half] = a * c - b * s
+        out[..., half:dims] = b * c + a * s
+    else:
+        a, b = v[..., 0:dims:2], v[..., 1:dims:2]
+        out[..., 0:dims:2] = a * c - b * s
+        out[..., 1:dims:2] = b * c + a * s
+    return out
+
+
+def latent_prep(proj, q_rank, kv_rank, rope_dim, q_gain, kv_gain, eps, positions, row_of_token, table, rot_dims,
+                pairing, pages, block_tables, cq, write=True):
+    n = proj.shape[0]
+    p = proj.float()
+    ql = p[:, :q_rank]
+    cq.copy_((ql / torch.sqrt(ql.pow(2).mean(-1, keepdim=True) + eps) * q_gain.float()).to(cq.dtype))
+    if not write:
+        return
+    kv = p[:, q_rank:q_rank + kv_rank]
+    c = kv / torch.sqrt(kv.pow(2).mean(-1, keepdim=True) + eps) * kv_gain.float()
+    kr = p[:, q_rank + kv_rank:q_rank + kv_rank + rope_dim]
+    pos = positions[:n].long()
+    if rot_dims:
+        kr = _rotate_pairs(kr, table[pos], rot_dims, pairing)
+    page_size = pages.shape[1]
+    page = block_tables[row_of_token[:n].long(), pos // page_size].long()
+    pages[page, pos % page_size] = torch.cat((c, kr), -1).to(pages.dtype)
+
+
+def rope_inplace(x, num_heads, head_stride, offset, rot_dims, pairing, positions, table):
+    n = x.shape[0]
+    cs = table[positions[:n].long()]
+    for h in range(num_heads):
+        lo = h * head_stride + offset
+        v = x[:, lo:lo + rot_dims].float()
+        x[:, lo:lo + rot_dims] = _rotate_pairs(v, cs, rot_dims, pairing).to(x.dtype)
+
+
+def latent_attention_scratch_bytes(num_tokens, num_heads, kv_rank, splits):
+    return 0 if splits <= 1 else num_tokens * num_heads * splits * (kv_rank + 2) * 4
+
+
+def latent_attention(qlat, q, rot_offset, head_stride, pages, block_tables, positions, row_of_token, out,
+                     num_heads, kv_rank, rope_dim, scale, splits=1, scratch=None):
+    h, n, r = qlat.shape
+    page_size = pages.shape[1]
+    for t in range(n):
+        pos, row = int(positions[t]), int(row_of_token[t])
+        keys = torch.arange(pos + 1)
+        vec = pages[block_tables[row, keys // page_size].long(), keys % page_size].float()  # [T, R + P]
+        qr = q[t].float().view(num_heads, head_stride)[:, rot_offset:rot_offset + rope_dim]
+        full = torch.cat((qlat[:, t].float(), qr), -1)  # [H, R + P]
+        w = torch.softmax(full @ vec.t() * scale, -1)
+        out[:, t] = (w @ vec[:, :kv_rank]).to(out.dtype)
+
+
+def heads_gate(ov, gate, out):
+    h, n, v = ov.shape
+    y = ov.float().permute(1, 0, 2).reshape(n, h * v)
+    if gate is not None:
+        y = y / (1 + torch.exp(-gate.float()))
+    out.copy_(y.to(out.dtype))
+
+
+def moe_tile_rows():
+    return 64
+
+
+def moe_max_tiles(num_pairs, num_experts, tile_rows):
+    return num_pairs // tile_rows + min(num_experts, num_pairs)
+
+
+def moe_route(logits, top, renormalize, ids, weights, offsets, perm, plan, max_tiles):
+    n, e = logits.shape
+    s = torch.softmax(logits.float(), -1)
+    chosen = torch.zeros(n, top, dtype=torch.long)
+    z = logits.clone()
+    for k in range(top):
+        chosen[:, k] = torch.argmax(z, -1)  # the first of equal maxima
+        z[torch.arange(n), chosen[:, k]] = float("-inf")
+    w = torch.gather(s, 1, chosen)
+    if renormalize:
+        w = w / w.sum(-1, keepdim=True)
+    ids.view(-1)[:n * top] = chosen.reshape(-1).to(torch.int32)
+    weights.view(-1)[:n * top] = w.reshape(-1)
+    flat = chosen.reshape(-1)
+    order = torch.argsort(flat, stable=True)
+    perm[:n * top] = order.to(torch.int32)
+    counts = torch.bincount(flat, minlength=e)
+    offsets[0] = 0
+    offsets[1:e + 1] = torch.cumsum(counts, 0).to(torch.int32)
+
+
+def moe_up(x, wgu, perm, offsets, plan, max_tiles, top, act, out):
+    e, ff2, k = wgu.shape
+    ff = ff2 // 2
+    off = offsets.tolist()
+    for ex in range(e):
+        lo, hi = off[ex], off[ex + 1]
+        if hi <= lo:
+            continue
+        rows = x[(perm[lo:hi] // top).long()].float()
+        y = (rows @ wgu[ex].float().t()).to(out.dtype).float()
+        out[lo:hi] = (_glu_activation(y[:, :ff], act) * y[:, ff:]).to(out.dtype)
+
+
+def moe_down(act, wdown, perm, offsets, plan, max_tiles, y):
+    e = wdown.shape[0]
+    off = offsets.tolist()
+    for ex in range(e):
+        lo, hi = off[ex], off[ex + 1]
+        if hi <= lo:
+            continue
+        y[perm[lo:hi].long()] = (act[lo:hi].float() @ wdown[ex].float().t()).to(act.dtype).float()
+
+
+def moe_combine(y, weights, out, top):
+    n, h = out.shape
+    out.copy_((y[:n * top].view(n, top, h) * weights.view(-1)[:n * top].view(n, top, 1)).sum(1).to(out.dtype))
+
+
 ALL = ["gemm_smallm", "gemm_smallm_gated", "check_status", "embedding", "add_rmsnorm", "silu_mul", "rope_table", "rope_kv_write",
-       "attention_scratch_bytes", "paged_attention", "argmax", "repetition_penalty", "sample"]
+       "attention_scratch_bytes", "paged_attention", "argmax", "repetition_penalty", "sample",
+       "stream_inject", "add_norm_grouped", "glu_act", "causal_taps", "latent_prep", "rope_inplace",
+       "latent_attention_scratch_bytes", "latent_attention", "heads_gate", "moe_tile_rows", "moe_max_tiles",
+       "moe_route", "moe_up", "moe_down", "moe_combine"]
 
 
 def install(monkeypatch) -> None:
