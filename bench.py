@@ -892,6 +892,152 @@ def run_reference(args) -> dict:
             + " | ".join(errors)[:600]}
 
 
+# ---------------------------------------------------------------------------------------
+# --workload damolorn: the latent-attention / routed-experts design beside the dense Qwen2 shape
+# of equal width, equal number of layer runs and equal active feed-forward width.
+
+DAMOLORN_SIZES = {
+    # width, heads, unrotated / rotated / value numbers per head, ranks, dense ff, experts / top / expert ff
+    "2k": dict(width=2048, heads=16, dim=128, rot=64, vdim=128, kv_rank=512, q_rank=768, dense_ff=8448,
+               experts=64, top=6, ff=1408),
+    "4k": dict(width=4096, heads=32, dim=128, rot=64, vdim=128, kv_rank=512, q_rank=1536, dense_ff=12288,
+               experts=32, top=4, ff=3072),
+}
+
+
+def damolorn_config(size: str, vocab: int = 32000) -> dict:
+    """Four layers of which the middle two run twice (six layer runs): a dense layer, three routed ones."""
+    z = DAMOLORN_SIZES[size]
+
+    def mixer(base):
+        return {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot"], "vdim": z["vdim"], "kv_rank": z["kv_rank"],
+                "q_rank": z["q_rank"], "rot": {"base": base, "dims": z["rot"]}, "scale": (z["dim"] + z["rot"]) ** -0.5}
+
+    moe = {"kind": "moe", "expert": {"ff": z["ff"]}, "router": {"experts": z["experts"], "top": z["top"]}}
+    layers = [{"type": "latent_attention", "mixer": mixer(10000.0), "mlp": {"kind": "dense", "ff": z["dense_ff"]}},
+              {"type": "latent_attention_2", "mixer": mixer(500000.0), "mlp": moe},
+              {"type": "latent_attention", "mixer": mixer(10000.0), "mlp": moe},
+              {"type": "latent_attention_2", "mixer": mixer(500000.0), "mlp": moe}]
+    return {"architecture": "Damolorn", "vocab": vocab, "width": z["width"], "norm": {"eps": 1e-5, "groups": 2},
+            "canon": {"taps": 4}, "layers": layers, "loop": {"start": 1, "stop": 3, "times": 2},
+            "max_positions": 8192}
+
+
+def run_damolorn(args) -> dict:
+    import torch
+
+    from emberserve_b200 import kernels as K
+    from emberserve_b200.config.damolorn import DamolornConfig
+    from emberserve_b200.config.model import Qwen2Config
+    from emberserve_b200.engine.runner import ModelRunner, StepRow
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA GPU"
+    peaks = measured_peaks()
+    K.library()
+    z = DAMOLORN_SIZES[args.damolorn_size]
+    dam = DamolornConfig.from_dict(damolorn_config(args.damolorn_size))
+    runs = len(dam.layer_runs())
+    qwen = Qwen2Config.from_dict(dict(
+        SHAPE_7B, vocab_size=32000, hidden_size=z["width"], num_attention_heads=z["heads"],
+        num_key_value_heads=max(1, z["heads"] // 8), head_dim=128, intermediate_size=z["top"] * z["ff"],
+        num_hidden_layers=runs, max_position_embeddings=8192, architectures=["Qwen2ForCausalLM"], model_type="qwen2"))
+    ctx_len, batches, prompts = args.decode_context if args.decode_context != CONTEXT else 2048, (8, 64), (512, 2048)
+    dtype = torch.float32 if args.dtype == "float32" else torch.bfloat16
+    gen = torch.Generator().manual_seed(1)
+
+    def kernel_times(fn) -> list:
+        from torch.profiler import ProfilerActivity, profile
+
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            fn()
+            torch.cuda.synchronize()
+        rows = sorted(prof.key_averages(), key=lambda e: -e.device_time_total)
+        total = sum(e.device_time_total for e in rows) or 1.0
+        return [{"kernel": e.key[:80], "calls": e.count, "us": round(e.device_time_total, 1),
+                 "share": round(e.device_time_total / total, 4)} for e in rows[:12]]
+
+    def measure(cfg, name: str) -> dict:
+        pages = max(batches) * (ctx_len // PAGE_SIZE + 2) + 2 * max(prompts) // PAGE_SIZE + 64
+        runner = ModelRunner.from_random(cfg, seed=0, dtype=dtype, device="cuda:0", page_size=PAGE_SIZE,
+                                         num_pages=pages, num_state_slots=max(batches) + 2, tiled_weight_copies=False)
+        for t in runner.storage.tensors:
+            t.normal_(0, 1)
+        vocab = cfg.vocab_size
+        out: dict = {"model": name, "parameters_gb": round(sum(
+            p.numel() * p.element_size() for p in runner.decoder.parameters().values()) / 1e9, 2)}
+
+        def prefill(ptoks: int, iters: int = 3) -> float:
+            times = []
+            for it in range(iters + 1):
+                runner.cache.admit(5000 + it, ptoks)
+                toks = torch.randint(0, vocab, (ptoks,), generator=gen).tolist()
+                ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                ev0.record()
+                runner.step([StepRow(5000 + it, toks, 0, [ptoks - 1])])
+                ev1.record()
+                torch.cuda.synchronize()
+                runner.cache.release(5000 + it)
+                if it:
+                    times.append(ev0.elapsed_time(ev1))
+            return statistics.mean(times)
+
+        def decode(batch: int, steps: int, warmup: int = 3) -> float:
+            start = ctx_len - steps - warmup
+            seqs = list(range(1000, 1000 + batch))
+            for sq in seqs:
+                runner.cache.admit(sq, start)
+                runner.cache.commit(sq, start)
+            toks = torch.randint(0, vocab, (batch, steps + warmup), generator=gen).tolist()
+
+            def one(i):
+                rows = []
+                for sq, t in zip(seqs, toks):
+                    runner.cache.extend(sq, start + i + 1)
+                    rows.append(StepRow(sq, [t[i]], start + i, [0]))
+                runner.step(rows)
+
+            for i in range(warmup):
+                one(i)
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            ev0.record()
+            for i in range(warmup, warmup + steps):
+                one(i)
+            ev1.record()
+            torch.cuda.synchronize()
+            for sq in seqs:
+                runner.cache.release(sq)
+            return ev0.elapsed_time(ev1) / steps
+
+        for t in prompts:
+            ms = prefill(t)
+            out[f"prefill_{t}_ms"] = round(ms, 3)
+            out[f"prefill_{t}_tok_s"] = round(t * 1e3 / ms)
+        out["prefill_kernels"] = kernel_times(lambda: prefill(max(prompts), 1))
+        if not args.no_graphs:
+            runner.enable_graphs(ctx_len + 64, max(batches))
+        for b in batches:
+            ms = decode(b, min(args.steps, 32))
+            out[f"decode_b{b}_ms"] = round(ms, 3)
+            out[f"decode_b{b}_tok_s"] = round(b * 1e3 / ms)
+        runner.use_graphs = False
+        out["decode_kernels"] = kernel_times(lambda: decode(max(batches), 2, 1))
+        runner.graphs = None
+        del runner
+        import gc
+
+        gc.collect()
+        torch.cuda.empty_cache()
+        return out
+
+    ours = measure(dam, "Damolorn")
+    beside = measure(qwen, "Qwen2 dense")
+    return {"workload": "damolorn", "size": args.damolorn_size, "dtype": args.dtype, "layer_runs": runs,
+            "context": ctx_len, "shape": z, "peaks": peaks, "damolorn": ours, "qwen2": beside,
+            "data": "synthetic: uniform random token ids, random weights N(0,0.02) seed 0"}
+
+
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("--gpus", type=int, default=1)
@@ -899,10 +1045,14 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--workload", choices=["decode-7b", "serve-0.5b", "mixed-32b", "fp32-7b"], default="decode-7b",
+    ap.add_argument("--workload", choices=["decode-7b", "serve-0.5b", "mixed-32b", "fp32-7b", "damolorn"],
+                    default="decode-7b",
                     help="decode-7b: the headline line; serve-0.5b: continuous batching of --requests requests; "
                          "mixed-32b: chunked prefill of long prompts beside decode at the 32B shape; fp32-7b: "
-                         "the true 32-bit path (the headline line runs the last three as child processes)")
+                         "the true 32-bit path (the headline line runs the last three as child processes); "
+                         "damolorn: prompt and decode steps of the Damolorn design at --damolorn-size beside the "
+                         "dense Qwen2 shape of equal width, layer runs and active feed-forward width")
+    ap.add_argument("--damolorn-size", choices=sorted(DAMOLORN_SIZES), default="2k")
     ap.add_argument("--no-extras", action="store_true",
                     help="the headline line without the points that need other models or kernels alone")
     ap.add_argument("--requests", type=int, default=256)
@@ -967,6 +1117,9 @@ def main() -> int:
         return 0
     if args.workload == "fp32-7b":
         print(json.dumps(run_fp32(args)))
+        return 0
+    if args.workload == "damolorn":
+        print(json.dumps(run_damolorn(args)))
         return 0
     result = run_reference(args) if args.impl == "reference" else run_ours(args)
     print(json.dumps(result))

@@ -14,7 +14,9 @@
 // attention itself with an optional split of the keys over several blocks, the merge of such
 // splits, and the output gate with the transposition back to token-major rows.
 // Scores, softmax and the weighted sums are 32-bit; T is the storage type (float or bfloat16).
-#include "common.cuh"
+// In bfloat16 the attention runs on the tensor cores where the sizes allow (latent_attention_mma.cu);
+// the kernel here serves the 32-bit path and every other geometry.
+#include "latent_attention.cuh"
 
 namespace ems {
 
@@ -411,12 +413,24 @@ EMS_EXPORT int ems_latent_attention(const void* qlat, const void* qrot, int q_ro
                                     int dtype, const void* pages, const int* block_tables, int bt_stride,
                                     int page_size, const int* positions, const int* row_of_token, void* out,
                                     int num_tokens, int H, int R, int P, float scale, int splits, void* scratch,
-                                    long long scratch_bytes, cudaStream_t stream) {
+                                    long long scratch_bytes, int impl, cudaStream_t stream) {
     if (num_tokens <= 0) return EMS_OK;
     if (splits < 1 || splits > 65535) return EMS_ERR_SHAPE;
     if (dtype == EMS_BF16 && ((R + P) % 2)) return EMS_ERR_SHAPE;  // a cached vector is read in 4-byte words
     if (splits > 1 && (!scratch || scratch_bytes < ems_latent_attention_scratch_bytes(num_tokens, H, R, splits)))
         return EMS_ERR_SCRATCH;
+    // impl: 0 the tensor-core kernel where it takes the case, 1 always the generic kernel
+    if (dtype == EMS_BF16 && impl == 0 &&
+        latent_mma_supported(R, P, qlat, qrot, q_row_stride, q_head_stride, pages)) {
+        const int rc = run_latent_mma(qlat, qrot, q_row_stride, q_head_stride, pages, block_tables, bt_stride,
+                                      page_size, positions, row_of_token, out, (float*)scratch, num_tokens, H, R, P,
+                                      scale, splits, stream);
+        if (rc != EMS_OK || splits == 1) return rc;
+        dim3 mg(num_tokens, H);
+        latent_attention_merge_kernel<bf16><<<mg, la_threads_for(R), 0, stream>>>((const float*)scratch, (bf16*)out,
+                                                                                  num_tokens, H, R, splits);
+        return launch_status();
+    }
     if (dtype == EMS_F32)
         return dispatch_latent_attention<float>(qlat, qrot, q_row_stride, q_head_stride, pages, block_tables,
                                                 bt_stride, page_size, positions, row_of_token, out, (float*)scratch,

@@ -1,0 +1,281 @@
+// Latent attention on the tensor cores (bfloat16): the same computation as the generic kernel of
+// latent_attention.cu, as two mma.sync m16n8k16 products per tile of keys.
+//
+// A block serves ONE token and up to 16 of its heads: the heads are the 16 rows of the m16 tile,
+// and all of them read the same cached vectors [c | krot] (R + P numbers per key), so a tile of
+// 64 keys in shared memory feeds both products:
+//   S[16, 64]  = Q[16, R + P] K^T          K rows as they lie in the cache (ldmatrix)
+//   O[16, R]  += P[16, 64] K[:, :R]        the same rows, read transposed (ldmatrix.trans)
+// Warp w computes the scores of keys 16 w .. 16 w + 15 of the tile and owns the latent columns
+// [w R / 4, (w + 1) R / 4) of O.  Scores, running maximum and sums are float32; the weights are
+// rounded to bfloat16 for the second product.  Tiles arrive through a two-stage cp.async ring;
+// rows past the last visible key are filled with zeros.  With `splits` > 1 a block takes a range
+// of the keys and leaves unnormalised sums, maximum and sum for the merge kernel.
+#include "latent_attention.cuh"
+
+namespace ems {
+
+constexpr int LM_KT = 64;     // keys per tile
+constexpr int LM_WARPS = 4;
+constexpr int LM_PAD = 8;     // bfloat16 of padding per shared-memory row
+
+__device__ __forceinline__ void lm_cp_async16(uint32_t dst, const void* src, bool valid) {
+    const int bytes = valid ? 16 : 0;  // 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void lm_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void lm_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ void lm_ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void lm_ldmatrix_x2_trans(uint32_t addr, uint32_t& r0, uint32_t& r1) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+__device__ __forceinline__ void lm_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// NTW: the most 8-column tiles of O a warp may own (R <= 32 * NTW).
+template <int NTW>
+__global__ void __launch_bounds__(LM_WARPS * 32)
+latent_attention_mma_kernel(const bf16* __restrict__ qlat, const bf16* __restrict__ qrot, int q_row_stride,
+                            int q_head_stride, const bf16* __restrict__ pages, const int* __restrict__ block_tables,
+                            int bt_stride, int page_size, const int* __restrict__ positions,
+                            const int* __restrict__ row_of_token, bf16* __restrict__ out, float* __restrict__ partial,
+                            int num_tokens, int H, int R, int P, float scale_log2, int splits) {
+    extern __shared__ __align__(16) unsigned char lm_smem[];
+    const int D = R + P, DS = D + LM_PAD;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+    const int t = blockIdx.x, sp = blockIdx.y, h0 = blockIdx.z * 16;
+    bf16* Qs = reinterpret_cast<bf16*>(lm_smem);                  // [16][DS]
+    bf16* Ks = Qs + 16 * DS;                                      // [2][LM_KT][DS]
+    bf16* Ps = Ks + 2 * LM_KT * DS;                               // [16][LM_KT + LM_PAD]
+    float* smax = reinterpret_cast<float*>(Ps + 16 * (LM_KT + LM_PAD));  // [LM_WARPS][16]
+    float* ssum = smax + LM_WARPS * 16;                           // [LM_WARPS][16]
+    constexpr int PS = LM_KT + LM_PAD;
+
+    const int qpos = positions[t];
+    const int* bt = block_tables + (size_t)row_of_token[t] * bt_stride;
+    const int kend = qpos + 1;
+    int chunk = (kend + splits - 1) / splits;
+    chunk = (chunk + LM_KT - 1) / LM_KT * LM_KT;
+    const int k_lo = sp * chunk, k_hi = min(kend, k_lo + chunk);
+    const int ntw = R / 32;                 // 8-column tiles of O per warp
+    const int col0 = warp * (R / LM_WARPS); // my first latent column
+
+    float o[NTW][4];
+#pragma unroll
+    for (int i = 0; i < NTW; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};  // rows g and g + 8
+
+    if (k_lo < k_hi) {
+        // the queries: row = head, [folded query (R) | rotated part (P)]
+        for (int k = threadIdx.x; k < 16 * (D / 2); k += blockDim.x) {
+            const int row = k / (D / 2), d = (k % (D / 2)) * 2;
+            uint32_t v = 0u;
+            if (h0 + row < H) {
+                const bf16* src = d < R ? qlat + ((size_t)(h0 + row) * num_tokens + t) * R + d
+                                        : qrot + (size_t)t * q_row_stride + (size_t)(h0 + row) * q_head_stride + (d - R);
+                v = *reinterpret_cast<const uint32_t*>(src);
+            }
+            *reinterpret_cast<uint32_t*>(Qs + row * DS + d) = v;
+        }
+        const int cpr = D / 8;  // 16-byte chunks per cached vector
+        const uint32_t ks_base = (uint32_t)__cvta_generic_to_shared(Ks);
+        auto prefetch = [&](int tile_k0, int stage) {
+            for (int c = threadIdx.x; c < LM_KT * cpr; c += blockDim.x) {
+                const int row = c / cpr, col = c % cpr;
+                const int key = tile_k0 + row;
+                const bool valid = key < k_hi;
+                const bf16* src = pages;
+                if (valid) src = pages + ((size_t)bt[key / page_size] * page_size + key % page_size) * D + col * 8;
+                lm_cp_async16(ks_base + (uint32_t)(((stage * LM_KT + row) * DS + col * 8) * 2), src, valid);
+            }
+            lm_commit();
+        };
+        const uint32_t qs_addr = (uint32_t)__cvta_generic_to_shared(Qs);
+        const uint32_t ps_addr = (uint32_t)__cvta_generic_to_shared(Ps);
+        // ldmatrix addresses of this lane: A tiles (row-major 16 x 16), B tiles of the score product
+        // (two key octets x two halves of 16 columns), B tiles of the second product (transposed)
+        const int a_row = (lane & 7) + 8 * ((lane >> 3) & 1), a_col = 8 * (lane >> 4);
+        const int b_row = (lane & 7) + 8 * (lane >> 4), b_col = 8 * ((lane >> 3) & 1);
+        const int v_row = (lane & 7) + 8 * ((lane >> 3) & 1);
+
+        prefetch(k_lo, 0);
+        int stage = 0;
+        for (int k0 = k_lo; k0 < k_hi; k0 += LM_KT, stage ^= 1) {
+            const bool more = k0 + LM_KT < k_hi;
+            if (more) {
+                prefetch(k0 + LM_KT, stage ^ 1);
+                lm_wait<1>();
+            } else {
+                lm_wait<0>();
+            }
+            __syncthreads();
+            const uint32_t kst = ks_base + (uint32_t)(stage * LM_KT * DS * 2);
+            // scores of my 16 keys
+            float s[2][4];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+            for (int kk = 0; kk < D; kk += 16) {
+                uint32_t a[4], b[4];
+                lm_ldmatrix_x4(qs_addr + (uint32_t)((a_row * DS + kk + a_col) * 2), a);
+                lm_ldmatrix_x4(kst + (uint32_t)(((warp * 16 + b_row) * DS + kk + b_col) * 2), b);
+                lm_mma(s[0], a, b[0], b[1]);
+                lm_mma(s[1], a, b[2], b[3]);
+            }
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = k0 + warp * 16 + j * 8 + 2 * tq + (e & 1);
+                    s[j][e] = key < k_hi ? s[j][e] * scale_log2 : -INFINITY;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], s[j][e]);
+                }
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+                if (tq == 0) smax[warp * 16 + g + 8 * r] = mx[r];
+            }
+            __syncthreads();
+            float alpha[2], sum[2] = {0.f, 0.f};
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                float mt = smax[g + 8 * r];
+#pragma unroll
+                for (int w = 1; w < LM_WARPS; ++w) mt = fmaxf(mt, smax[w * 16 + g + 8 * r]);
+                const float m_new = fmaxf(m_run[r], mt);  // finite: key k0 of the tile is visible
+                alpha[r] = exp2f(m_run[r] - m_new);
+                m_run[r] = m_new;
+            }
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                float p[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    p[e] = exp2f(s[j][e] - m_run[e >> 1]);
+                    sum[e >> 1] += p[e];
+                }
+                const int col = warp * 16 + j * 8 + 2 * tq;
+                *reinterpret_cast<__nv_bfloat162*>(Ps + g * PS + col) = __floats2bfloat162_rn(p[0], p[1]);
+                *reinterpret_cast<__nv_bfloat162*>(Ps + (g + 8) * PS + col) = __floats2bfloat162_rn(p[2], p[3]);
+            }
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
+                sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
+                if (tq == 0) ssum[warp * 16 + g + 8 * r] = sum[r];
+            }
+            __syncthreads();
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                float st = 0.f;
+#pragma unroll
+                for (int w = 0; w < LM_WARPS; ++w) st += ssum[w * 16 + g + 8 * r];
+                l_run[r] = l_run[r] * alpha[r] + st;
+            }
+#pragma unroll
+            for (int i = 0; i < NTW; ++i) {
+                o[i][0] *= alpha[0];
+                o[i][1] *= alpha[0];
+                o[i][2] *= alpha[1];
+                o[i][3] *= alpha[1];
+            }
+            // O += P K[:, my columns]
+#pragma unroll
+            for (int kk = 0; kk < LM_KT; kk += 16) {
+                uint32_t a[4];
+                lm_ldmatrix_x4(ps_addr + (uint32_t)((a_row * PS + kk + a_col) * 2), a);
+#pragma unroll
+                for (int i = 0; i < NTW; ++i) {
+                    if (i < ntw) {
+                        uint32_t b0, b1;
+                        lm_ldmatrix_x2_trans(kst + (uint32_t)(((kk + v_row) * DS + col0 + i * 8) * 2), b0, b1);
+                        lm_mma(o[i], a, b0, b1);
+                    }
+                }
+            }
+            __syncthreads();  // the tile and Ps are free for the next round
+        }
+    }
+    // results: rows g and g + 8 of this lane, columns col0 + 8 i + 2 tq, + 1
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int h = h0 + g + 8 * r;
+        if (h >= H) continue;
+        if (splits == 1) {
+            const float inv = 1.f / l_run[r];
+            bf16* dst = out + ((size_t)h * num_tokens + t) * R;
+#pragma unroll
+            for (int i = 0; i < NTW; ++i)
+                if (i < ntw)
+                    *reinterpret_cast<__nv_bfloat162*>(dst + col0 + i * 8 + 2 * tq) =
+                        __floats2bfloat162_rn(o[i][2 * r] * inv, o[i][2 * r + 1] * inv);
+        } else {
+            float* dst = partial + (((size_t)t * H + h) * splits + sp) * (R + 2);
+#pragma unroll
+            for (int i = 0; i < NTW; ++i)
+                if (i < ntw) {
+                    dst[col0 + i * 8 + 2 * tq] = o[i][2 * r];
+                    dst[col0 + i * 8 + 2 * tq + 1] = o[i][2 * r + 1];
+                }
+            if (warp == 0 && tq == 0) {
+                // the merge kernel works in natural-log units
+                dst[R] = m_run[r] * 0.6931471805599453f;
+                dst[R + 1] = l_run[r];
+            }
+        }
+    }
+}
+
+bool latent_mma_supported(int R, int P, const void* qlat, const void* qrot, int q_row_stride, int q_head_stride,
+                          const void* pages) {
+    const int D = R + P;
+    if (R % 32 || P % 16 || R > 512 || R < 32) return false;
+    if ((reinterpret_cast<uintptr_t>(pages) & 15) || (reinterpret_cast<uintptr_t>(qlat) & 3) ||
+        (reinterpret_cast<uintptr_t>(qrot) & 3) || (q_row_stride & 1) || (q_head_stride & 1))
+        return false;
+    const size_t smem = (size_t)(16 + 2 * LM_KT) * (D + LM_PAD) * 2 + 16 * (LM_KT + LM_PAD) * 2 + 2 * LM_WARPS * 16 * 4;
+    return smem <= 220 * 1024;
+}
+
+template <int NTW>
+static int launch_latent_mma(const void* qlat, const void* qrot, int q_row_stride, int q_head_stride,
+                             const void* pages, const int* block_tables, int bt_stride, int page_size,
+                             const int* positions, const int* row_of_token, void* out, float* partial,
+                             int num_tokens, int H, int R, int P, float scale, int splits, cudaStream_t stream) {
+    const int D = R + P;
+    const size_t smem = (size_t)(16 + 2 * LM_KT) * (D + LM_PAD) * 2 + 16 * (LM_KT + LM_PAD) * 2 + 2 * LM_WARPS * 16 * 4;
+    auto kern = latent_attention_mma_kernel<NTW>;
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+        cudaGetLastError();
+        return EMS_ERR_LAUNCH;
+    }
+    dim3 grid(num_tokens, splits, (H + 15) / 16);
+    kern<<<grid, LM_WARPS * 32, smem, stream>>>((const bf16*)qlat, (const bf16*)qrot, q_row_stride, q_head_stride,
+                                                (const bf16*)pages, block_tables, bt_stride, page_size, positions,
+                                                row_of_token, (bf16*)out, partial, num_tokens, H, R, P,
+                                                scale * 1.4426950408889634f, splits);
+    return launch_status();
+}
+
+int run_latent_mma(const void* qlat, const void* qrot, int q_row_stride, int q_head_stride, const void* pages,
+                   const int* block_tables, int bt_stride, int page_size, const int* positions,
+                   const int* row_of_token, void* out, float* partial, int num_tokens, int H, int R, int P,
+                   float scale, int splits, cudaStream_t stream) {
+#define EMS_LM(N)                                                                                                \
+    return launch_latent_mma<N>(qlat, qrot, q_row_stride, q_head_stride, pages, block_tables, bt_stride, page_size, \
+                                positions, row_of_token, out, partial, num_tokens, H, R, P, scale, splits, stream)
+    if (R <= 128) EMS_LM(4);
+    if (R <= 256) EMS_LM(8);
+    EMS_LM(16);
+#undef EMS_LM
+}
+
+}  // namespace ems

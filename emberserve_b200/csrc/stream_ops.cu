@@ -167,6 +167,28 @@ __global__ void causal_taps_state_kernel(const T* __restrict__ x, float* __restr
     }
 }
 
+// A step in which every row brings one token: convolution and state in one kernel.  A thread owns
+// (row, channel), reads the state it then rewrites.
+template <typename T>
+__global__ void causal_taps_single_kernel(const T* __restrict__ x, const void* __restrict__ w, int w_dtype,
+                                          float* __restrict__ state, const int* __restrict__ slots,
+                                          T* __restrict__ out, int C, int taps) {
+    const int row = blockIdx.x;
+    float* st = state + (size_t)slots[row] * (taps - 1) * C;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        const float h = to_f32<T>(x[(size_t)row * C + c]);
+        float conv = 0.f;
+        for (int j = 0; j < taps - 1; ++j) {
+            const float v = st[(size_t)j * C + c];
+            conv += load_any(w, w_dtype, (size_t)c * taps + j) * v;
+            if (j > 0) st[(size_t)(j - 1) * C + c] = v;
+        }
+        conv += load_any(w, w_dtype, (size_t)c * taps + taps - 1) * h;
+        st[(size_t)(taps - 2) * C + c] = h;
+        out[(size_t)row * C + c] = from_f32<T>(h + conv);
+    }
+}
+
 static int threads_for(int n) {
     int t = 32;
     while (t < n && t < 256) t <<= 1;
@@ -236,6 +258,11 @@ EMS_EXPORT int ems_causal_taps(const void* x, const void* w, int w_dtype, void* 
     const int th = threads_for(C);
 #define EMS_LAUNCH_TAPS(T)                                                                                   \
     do {                                                                                                     \
+        if (n == rows && taps > 1) {                                                                         \
+            causal_taps_single_kernel<T><<<rows, th, 0, stream>>>((const T*)x, w, w_dtype, (float*)state,    \
+                                                                  slots, (T*)out, C, taps);                  \
+            break;                                                                                           \
+        }                                                                                                    \
         causal_taps_kernel<T><<<n, th, 0, stream>>>((const T*)x, w, w_dtype, (const float*)state, slots,     \
                                                     cu_q, row_of_token, (T*)out, C, taps);                  \
         if (taps > 1)                                                                                        \

@@ -78,7 +78,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "ems_causal_taps": [P, P, I, P, P, P, P, P, I, I, I, I, I, P],
         "ems_latent_prep": [P, I, I, I, I, I, I, P, P, I, F, P, P, P, I, I, P, P, I, I, P, I, P],
         "ems_rope_inplace": [P, I, I, I, I, I, I, I, I, P, P, P],
-        "ems_latent_attention": [P, P, I, I, I, P, P, I, I, P, P, P, I, I, I, I, F, I, P, L, P],
+        "ems_latent_attention": [P, P, I, I, I, P, P, I, I, P, P, P, I, I, I, I, F, I, P, L, I, P],
         "ems_heads_gate": [P, P, I, P, I, I, I, I, P],
         "ems_moe_route": [P, I, I, I, I, P, P, P, P, P, I, P],
         "ems_moe_up": [P, P, I, P, P, I, I, I, I, I, P, P],
@@ -381,13 +381,15 @@ def latent_attention_scratch_bytes(num_tokens: int, num_heads: int, kv_rank: int
 def latent_attention(qlat: torch.Tensor, q: torch.Tensor, rot_offset: int, head_stride: int, pages: torch.Tensor,
                      block_tables: torch.Tensor, positions: torch.Tensor, row_of_token: torch.Tensor,
                      out: torch.Tensor, num_heads: int, kv_rank: int, rope_dim: int, scale: float,
-                     splits: int = 1, scratch: torch.Tensor | None = None) -> None:
+                     splits: int = 1, scratch: torch.Tensor | None = None, kernel: str = "auto") -> None:
     """Causal attention over cached latent vectors.  qlat: [H, N, kv_rank], the queries folded into
     the latent space; q: [N, H * head_stride] whose `rope_dim` numbers from `rot_offset` on in every
     head are the rotated query part; pages: [num_pages, page_size, kv_rank + rope_dim].
     out[h, n, :] = sum_j softmax_j((qlat[h, n] . c_j + qrot[n, h] . krot_j) * scale) c_j over the
     keys j <= position of token n of its request.  `splits` > 1 cuts every token's keys over
-    that many blocks (`scratch` takes the partial sums; a merge kernel follows)."""
+    that many blocks (`scratch` takes the partial sums; a merge kernel follows).  In bfloat16 the
+    tensor-core kernel runs where it takes the sizes (kv_rank a multiple of 32 up to 512, rope_dim a
+    multiple of 16); kernel="generic" keeps the CUDA-core kernel (tests compare the two)."""
     h, n, r = qlat.shape
     assert h == num_heads and r == kv_rank and out.shape == qlat.shape and pages.shape[2] == kv_rank + rope_dim
     assert qlat.dtype == q.dtype == out.dtype == pages.dtype and q.stride(1) == 1
@@ -398,8 +400,8 @@ def latent_attention(qlat: torch.Tensor, q: torch.Tensor, rot_offset: int, head_
         _ptr(pages, "pages"), _i32(block_tables, "block_tables"), block_tables.shape[1], pages.shape[1],
         _i32(positions, "positions"), _i32(row_of_token, "row_of_token"), _ptr(out, "out"), n, num_heads, kv_rank,
         rope_dim, float(scale), splits, _ptr(scratch, "scratch"),
-        0 if scratch is None else scratch.numel() * scratch.element_size(), _stream()),
-        "latent_attention", 2 if splits > 1 else 1)
+        0 if scratch is None else scratch.numel() * scratch.element_size(), 1 if kernel == "generic" else 0,
+        _stream()), "latent_attention", 2 if splits > 1 else 1)
 
 
 def heads_gate(ov: torch.Tensor, gate: torch.Tensor | None, out: torch.Tensor) -> None:

@@ -331,7 +331,7 @@ def latent_attention_scratch_bytes(num_tokens, num_heads, kv_rank, splits):
 
 
 def latent_attention(qlat, q, rot_offset, head_stride, pages, block_tables, positions, row_of_token, out,
-                     num_heads, kv_rank, rope_dim, scale, splits=1, scratch=None):
+                     num_heads, kv_rank, rope_dim, scale, splits=1, scratch=None, kernel="auto"):
     h, n, r = qlat.shape
     page_size = pages.shape[1]
     for t in range(n):
