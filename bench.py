@@ -1010,6 +1010,12 @@ def run_damolorn(args) -> dict:
                 runner.cache.release(sq)
             return ev0.elapsed_time(ev1) / steps
 
+        if args.only in ("prefill", "decode"):  # one phase of this model alone (for profiling)
+            if args.only == "prefill":
+                out["prefill_tokens"], out["prefill_ms"] = args.prefill_tokens, round(prefill(args.prefill_tokens, 1), 3)
+            else:
+                out["batch"], out["decode_ms"] = args.batch, round(decode(args.batch, 2, 1), 3)
+            return out
         for t in prompts:
             ms = prefill(t)
             out[f"prefill_{t}_ms"] = round(ms, 3)
@@ -1031,6 +1037,9 @@ def run_damolorn(args) -> dict:
         torch.cuda.empty_cache()
         return out
 
+    if args.only in ("prefill", "decode"):
+        return {"workload": "damolorn", "size": args.damolorn_size, "only": args.only,
+                "damolorn": measure(dam, "Damolorn")}
     ours = measure(dam, "Damolorn")
     beside = measure(qwen, "Qwen2 dense")
     return {"workload": "damolorn", "size": args.damolorn_size, "dtype": args.dtype, "layer_runs": runs,
@@ -1106,6 +1115,9 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.workload == "damolorn":
+        print(json.dumps(run_damolorn(args)))
+        return 0
     if args.only == "kernel":
         print(json.dumps(run_kernel(args)))
         return 0

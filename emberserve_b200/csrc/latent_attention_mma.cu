@@ -117,16 +117,37 @@ latent_attention_mma_kernel(const bf16* __restrict__ qlat, const bf16* __restric
             __syncthreads();
             const uint32_t kst = ks_base + (uint32_t)(stage * LM_KT * DS * 2);
             // scores of my 16 keys
-            float s[2][4];
+            float s[2][4], s2[2][4];  // two sets of sums over alternating slices of D: four chains in flight
 #pragma unroll
-            for (int j = 0; j < 2; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
-            for (int kk = 0; kk < D; kk += 16) {
+            for (int j = 0; j < 2; ++j) {
+                s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+                s2[j][0] = s2[j][1] = s2[j][2] = s2[j][3] = 0.f;
+            }
+            const uint32_t qa = qs_addr + (uint32_t)((a_row * DS + a_col) * 2);
+            const uint32_t kb = kst + (uint32_t)(((warp * 16 + b_row) * DS + b_col) * 2);
+            int kk = 0;
+            for (; kk + 32 <= D; kk += 32) {
+                uint32_t a[4], b[4], a2[4], b2[4];
+                lm_ldmatrix_x4(qa + kk * 2, a);
+                lm_ldmatrix_x4(kb + kk * 2, b);
+                lm_ldmatrix_x4(qa + (kk + 16) * 2, a2);
+                lm_ldmatrix_x4(kb + (kk + 16) * 2, b2);
+                lm_mma(s[0], a, b[0], b[1]);
+                lm_mma(s[1], a, b[2], b[3]);
+                lm_mma(s2[0], a2, b2[0], b2[1]);
+                lm_mma(s2[1], a2, b2[2], b2[3]);
+            }
+            if (kk < D) {
                 uint32_t a[4], b[4];
-                lm_ldmatrix_x4(qs_addr + (uint32_t)((a_row * DS + kk + a_col) * 2), a);
-                lm_ldmatrix_x4(kst + (uint32_t)(((warp * 16 + b_row) * DS + kk + b_col) * 2), b);
+                lm_ldmatrix_x4(qa + kk * 2, a);
+                lm_ldmatrix_x4(kb + kk * 2, b);
                 lm_mma(s[0], a, b[0], b[1]);
                 lm_mma(s[1], a, b[2], b[3]);
             }
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[j][e] += s2[j][e];
             float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
             for (int j = 0; j < 2; ++j)

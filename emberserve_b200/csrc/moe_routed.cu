@@ -11,9 +11,9 @@
 //   down      y[pair(i), :] = act[i, :] Wd[e]^T            (32-bit, in pair order)
 //   combine   out[t, :] = sum_k weight[t, k] * y[t * top + k, :]   (k ascending: a fixed order)
 //
-// A row of a product is computed by one thread column over K in ascending order, whatever else
-// is in its tile: a token's result does not depend on the batch.  Products accumulate in 32 bits
-// on the CUDA cores for both storage types.
+// A row of a product is accumulated over K in a fixed order, whatever else is in its tile: a
+// token's result does not depend on the batch.  Products accumulate in 32 bits: on the tensor
+// cores in bfloat16 (mma.sync), on the CUDA cores in the true 32-bit path.
 #include "common.cuh"
 
 namespace ems {
@@ -82,6 +82,70 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int n, int E,
             const int e = ids[(size_t)t * top + k];
             perm[offs[e] + atomicAdd(&cursor[e], 1)] = t * top + k;
         }
+}
+
+// The same in three kernels for steps of many tokens: one thread per token chooses and counts
+// (counts in global memory, zeroed before), one block lays out offsets and tiles, one thread per
+// pair takes its place among its expert's rows.
+__device__ __forceinline__ void moe_choose(const float* __restrict__ z, int E, int top, int renorm,
+                                           int* __restrict__ ids, float* __restrict__ wts, int* counts) {
+    float mx = -INFINITY;
+    for (int e = 0; e < E; ++e) mx = fmaxf(mx, z[e]);
+    float sum = 0.f;
+    for (int e = 0; e < E; ++e) sum += expf(z[e] - mx);
+    float chosen_sum = 0.f;
+    for (int k = 0; k < top; ++k) {
+        int best = -1;
+        float bv = -INFINITY;
+        for (int e = 0; e < E; ++e) {
+            bool taken = false;
+            for (int j = 0; j < k; ++j) taken |= ids[j] == e;
+            if (!taken && (best < 0 || z[e] > bv)) {
+                best = e;
+                bv = z[e];
+            }
+        }
+        ids[k] = best;
+        const float s = expf(bv - mx) / sum;
+        wts[k] = s;
+        chosen_sum += s;
+        atomicAdd(&counts[best], 1);
+    }
+    if (renorm)
+        for (int k = 0; k < top; ++k) wts[k] /= chosen_sum;
+}
+
+__global__ void moe_choose_kernel(const float* __restrict__ logits, int n, int E, int top, int renorm,
+                                  int* __restrict__ ids, float* __restrict__ wts, int* __restrict__ counts) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t < n) moe_choose(logits + (size_t)t * E, E, top, renorm, ids + (size_t)t * top, wts + (size_t)t * top, counts);
+}
+
+// offsets: [E + 1]; counts and cursor: [E] each (the cursors are set to zero here)
+__global__ void moe_plan_kernel(int E, const int* __restrict__ counts, int* __restrict__ cursor,
+                                int* __restrict__ offsets, int* __restrict__ plan, int max_tiles) {
+    if (threadIdx.x != 0) return;
+    int run = 0, nt = 0;
+    for (int e = 0; e < E; ++e) {
+        offsets[e] = run;
+        cursor[e] = 0;
+        for (int r0 = 0; r0 < counts[e] && nt < max_tiles; r0 += MOE_TM, ++nt) {
+            plan[1 + 3 * nt] = e;
+            plan[2 + 3 * nt] = run + r0;
+            plan[3 + 3 * nt] = min(MOE_TM, counts[e] - r0);
+        }
+        run += counts[e];
+    }
+    offsets[E] = run;
+    plan[0] = nt;
+}
+
+__global__ void moe_scatter_kernel(const int* __restrict__ ids, int pairs, const int* __restrict__ offsets,
+                                   int* __restrict__ cursor, int* __restrict__ perm) {
+    const int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= pairs) return;
+    const int e = ids[p];
+    perm[offsets[e] + atomicAdd(&cursor[e], 1)] = p;
 }
 
 __device__ __forceinline__ float moe_activation(float g, int act) {
@@ -170,6 +234,154 @@ moe_grouped_kernel(const T* __restrict__ a, const T* __restrict__ w, const int* 
     }
 }
 
+
+// ---------------------------------------------------------------------------------------
+// The same two products on the tensor cores (bfloat16, mma.sync m16n8k16, float32 accumulators).
+// A block computes 64 sorted rows x 128 weight rows through a three-stage cp.async ring of
+// 32-column slices; the activations' rows are gathered through the pair list as they are copied.
+// GLU: the 128 weight rows are 64 gate rows and the 64 up rows of the same outputs, and a warp
+// holds both halves of its outputs, so the activation is applied in registers.
+
+constexpr int MM_TM = 64, MM_TB = 128, MM_TK = 32, MM_PAD = 8, MM_STAGES = 3;
+
+__device__ __forceinline__ void mm_cp_async16(uint32_t dst, const void* src, bool valid) {
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void mm_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void mm_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ void mm_ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mm_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <bool GLU>
+__global__ void __launch_bounds__(256)
+moe_grouped_mma_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, const int* __restrict__ perm,
+                       const int* __restrict__ plan, int top, int N, int K, int act, bf16* __restrict__ out_t,
+                       float* __restrict__ out_f) {
+    constexpr int LDS = MM_TK + MM_PAD;  // elements per shared-memory row
+    __shared__ __align__(16) bf16 As[MM_STAGES][MM_TM][LDS];
+    __shared__ __align__(16) bf16 Bs[MM_STAGES][MM_TB][LDS];
+    __shared__ int src_row[MM_TM];
+    const int tile = blockIdx.x;
+    if (tile >= plan[0]) return;
+    const int e = plan[1 + 3 * tile], row0 = plan[2 + 3 * tile], rows = plan[3 + 3 * tile];
+    constexpr int NOUT = GLU ? MM_TB / 2 : MM_TB;  // output columns of a block
+    const int n0 = blockIdx.y * NOUT;
+    const bf16* we = w + (size_t)e * (GLU ? 2 : 1) * N * K;
+    for (int i = threadIdx.x; i < MM_TM; i += blockDim.x)
+        src_row[i] = i < rows ? (GLU ? perm[row0 + i] / top : row0 + i) : -1;
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int wm = warp >> 2, wn = warp & 3;  // 2 x 4 warps: 32 rows x (GLU ? 16 + 16 : 32) weight rows each
+    const uint32_t as_base = (uint32_t)__cvta_generic_to_shared(&As[0][0][0]);
+    const uint32_t bs_base = (uint32_t)__cvta_generic_to_shared(&Bs[0][0][0]);
+    const int ktiles = (K + MM_TK - 1) / MM_TK;
+
+    auto load = [&](int kt, int stage) {
+        const int k0 = kt * MM_TK;
+        {   // activations: 64 rows x 4 chunks, one per thread
+            const int r = threadIdx.x >> 2, c = (threadIdx.x & 3) * 8;
+            const int ar = src_row[r];
+            const bool ok = ar >= 0 && k0 + c < K;
+            mm_cp_async16(as_base + (uint32_t)(((stage * MM_TM + r) * LDS + c) * 2),
+                          ok ? a + (size_t)ar * K + k0 + c : a, ok);
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {  // weights: 128 rows x 4 chunks
+            const int idx = threadIdx.x + i * 256;
+            const int r = idx >> 2, c = (idx & 3) * 8;
+            int nn;  // the weight row that lands in shared row r
+            if (GLU) nn = r < NOUT ? n0 + r : N + n0 + (r - NOUT);
+            else nn = n0 + r;
+            const bool ok = (GLU ? (n0 + (r % NOUT) < N) : (nn < N)) && k0 + c < K;
+            mm_cp_async16(bs_base + (uint32_t)(((stage * MM_TB + r) * LDS + c) * 2),
+                          ok ? we + (size_t)nn * K + k0 + c : we, ok);
+        }
+    };
+
+    float acc[2][4][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
+
+    for (int s = 0; s < MM_STAGES - 1; ++s) {
+        if (s < ktiles) load(s, s);
+        mm_commit();
+    }
+    const int a_row = (lane & 7) + 8 * ((lane >> 3) & 1), a_col = 8 * (lane >> 4);
+    const int b_row = (lane & 7) + 8 * (lane >> 4), b_col = 8 * ((lane >> 3) & 1);
+    for (int kt = 0; kt < ktiles; ++kt) {
+        mm_wait<MM_STAGES - 2>();
+        __syncthreads();
+        if (kt + MM_STAGES - 1 < ktiles) load(kt + MM_STAGES - 1, (kt + MM_STAGES - 1) % MM_STAGES);
+        mm_commit();
+        const int stage = kt % MM_STAGES;
+#pragma unroll
+        for (int kk = 0; kk < MM_TK; kk += 16) {
+            uint32_t af[2][4], bf[2][4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+                mm_ldmatrix_x4(as_base + (uint32_t)(((stage * MM_TM + wm * 32 + i * 16 + a_row) * LDS + kk + a_col) * 2),
+                               af[i]);
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                // GLU: j = 0 the warp's 16 gate rows, j = 1 its 16 up rows; else 32 consecutive rows
+                const int brow = GLU ? (j * NOUT + wn * 16) : (wn * 32 + j * 16);
+                mm_ldmatrix_x4(bs_base + (uint32_t)(((stage * MM_TB + brow + b_row) * LDS + kk + b_col) * 2), bf[j]);
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    mm_mma(acc[i][2 * j], af[i], bf[j][0], bf[j][1]);
+                    mm_mma(acc[i][2 * j + 1], af[i], bf[j][2], bf[j][3]);
+                }
+        }
+    }
+    mm_wait<0>();
+    const int g = lane >> 2, tq = lane & 3;
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int hrow = 0; hrow < 2; ++hrow) {
+            const int r = wm * 32 + i * 16 + g + 8 * hrow;
+            if (r >= rows) continue;
+            if (GLU) {
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int x = 0; x < 2; ++x) {
+                        const int c = n0 + wn * 16 + nt * 8 + 2 * tq + x;
+                        if (c >= N) continue;
+                        const float gv = round_to<bf16>(acc[i][nt][2 * hrow + x]);
+                        const float uv = round_to<bf16>(acc[i][2 + nt][2 * hrow + x]);
+                        out_t[(size_t)(row0 + r) * N + c] = from_f32<bf16>(moe_activation(gv, act) * uv);
+                    }
+            } else {
+                float* dst = out_f + (size_t)perm[row0 + r] * N;
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                    for (int x = 0; x < 2; ++x) {
+                        const int c = n0 + wn * 32 + nt * 8 + 2 * tq + x;
+                        if (c < N) dst[c] = round_to<bf16>(acc[i][nt][2 * hrow + x]);
+                    }
+            }
+        }
+}
+
+static bool moe_mma_ok(const void* a, const void* w, int K) {
+    return K % 8 == 0 && !(reinterpret_cast<uintptr_t>(a) & 15) && !(reinterpret_cast<uintptr_t>(w) & 15);
+}
+
 template <typename T>
 __global__ void moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ wts, T* __restrict__ out,
                                    int top, int H) {
@@ -193,6 +405,15 @@ EMS_EXPORT int ems_moe_route(const float* logits, int n, int E, int top, int ren
     if (top < 1 || top > E) return EMS_ERR_SHAPE;
     const size_t smem = (size_t)(3 * E + 1) * sizeof(int);
     if (smem > 48 * 1024) return EMS_ERR_SHAPE;
+    if (n > 512) {  // `offsets` holds [offsets (E + 1) | counts (E) | cursors (E)]
+        int* counts = offsets + E + 1;
+        int* cursor = counts + E;
+        if (cudaMemsetAsync(counts, 0, (size_t)E * sizeof(int), stream) != cudaSuccess) return EMS_ERR_LAUNCH;
+        moe_choose_kernel<<<(n + 127) / 128, 128, 0, stream>>>(logits, n, E, top, renorm, ids, wts, counts);
+        moe_plan_kernel<<<1, 32, 0, stream>>>(E, counts, cursor, offsets, plan, max_tiles);
+        moe_scatter_kernel<<<(n * top + 255) / 256, 256, 0, stream>>>(ids, n * top, offsets, cursor, perm);
+        return launch_status();
+    }
     int th = 32;
     while (th < n && th < 1024) th <<= 1;
     moe_route_kernel<<<1, th, smem, stream>>>(logits, n, E, top, renorm, ids, wts, offsets, perm, plan, max_tiles);
@@ -200,8 +421,15 @@ EMS_EXPORT int ems_moe_route(const float* logits, int n, int E, int top, int ren
 }
 
 EMS_EXPORT int ems_moe_up(const void* x, const void* wgu, int dtype, const int* perm, const int* plan, int max_tiles,
-                          int top, int ff, int K, int act, void* out, cudaStream_t stream) {
+                          int top, int ff, int K, int act, void* out, int impl, cudaStream_t stream) {
     if (max_tiles <= 0) return EMS_OK;
+    // impl: 0 the tensor-core kernel where it takes the case, 1 always the CUDA-core kernel
+    if (dtype == EMS_BF16 && impl == 0 && moe_mma_ok(x, wgu, K)) {
+        dim3 mg(max_tiles, (ff + MM_TB / 2 - 1) / (MM_TB / 2));
+        moe_grouped_mma_kernel<true><<<mg, 256, 0, stream>>>((const bf16*)x, (const bf16*)wgu, perm, plan, top, ff, K,
+                                                             act, (bf16*)out, nullptr);
+        return launch_status();
+    }
     dim3 grid(max_tiles, (ff + MOE_TN - 1) / MOE_TN);
     if (dtype == EMS_F32)
         moe_grouped_kernel<float, true><<<grid, 256, 0, stream>>>((const float*)x, (const float*)wgu, perm, plan, top,
@@ -215,8 +443,14 @@ EMS_EXPORT int ems_moe_up(const void* x, const void* wgu, int dtype, const int* 
 }
 
 EMS_EXPORT int ems_moe_down(const void* a, const void* wdown, int dtype, const int* perm, const int* plan,
-                            int max_tiles, int H, int ff, float* y, cudaStream_t stream) {
+                            int max_tiles, int H, int ff, float* y, int impl, cudaStream_t stream) {
     if (max_tiles <= 0) return EMS_OK;
+    if (dtype == EMS_BF16 && impl == 0 && moe_mma_ok(a, wdown, ff)) {
+        dim3 mg(max_tiles, (H + MM_TB - 1) / MM_TB);
+        moe_grouped_mma_kernel<false><<<mg, 256, 0, stream>>>((const bf16*)a, (const bf16*)wdown, perm, plan, 1, H, ff,
+                                                              0, nullptr, y);
+        return launch_status();
+    }
     dim3 grid(max_tiles, (H + MOE_TN - 1) / MOE_TN);
     if (dtype == EMS_F32)
         moe_grouped_kernel<float, false><<<grid, 256, 0, stream>>>((const float*)a, (const float*)wdown, perm, plan, 1,

@@ -81,8 +81,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         "ems_latent_attention": [P, P, I, I, I, P, P, I, I, P, P, P, I, I, I, I, F, I, P, L, I, P],
         "ems_heads_gate": [P, P, I, P, I, I, I, I, P],
         "ems_moe_route": [P, I, I, I, I, P, P, P, P, P, I, P],
-        "ems_moe_up": [P, P, I, P, P, I, I, I, I, I, P, P],
-        "ems_moe_down": [P, P, I, P, P, I, I, I, P, P],
+        "ems_moe_up": [P, P, I, P, P, I, I, I, I, I, P, I, P],
+        "ems_moe_down": [P, P, I, P, P, I, I, I, P, I, P],
         "ems_moe_combine": [P, P, P, I, I, I, I, P],
     }
     for name, args in sigs.items():
@@ -430,37 +430,40 @@ def moe_route(logits: torch.Tensor, top: int, renormalize: bool, ids: torch.Tens
               offsets: torch.Tensor, perm: torch.Tensor, plan: torch.Tensor, max_tiles: int) -> None:
     """From router logits [N, E] (float32): softmax over all experts, the `top` largest per token
     (ids, weights: [N, top]; the weights are the scores, divided by their sum if `renormalize`),
-    the first sorted row of every expert (offsets [E + 1]), the pairs t * top + k in expert order
+    the first sorted row of every expert (offsets [E + 1], in a buffer of 3 E + 1: counters follow),
+    the pairs t * top + k in expert order
     (perm [N * top]) and the tiles of the grouped products (plan: count, then expert / first row /
     rows per tile)."""
     n, e = logits.shape
     assert logits.dtype == torch.float32 and weights.dtype == torch.float32
     assert ids.numel() >= n * top and weights.numel() >= n * top and perm.numel() >= n * top
-    assert offsets.numel() >= e + 1 and plan.numel() >= 1 + 3 * max_tiles
+    assert offsets.numel() >= 3 * e + 1 and plan.numel() >= 1 + 3 * max_tiles
     _check(library().ems_moe_route(_ptr(logits, "logits"), n, e, top, 1 if renormalize else 0, _i32(ids, "ids"),
                                    _ptr(weights, "weights"), _i32(offsets, "offsets"), _i32(perm, "perm"),
                                    _i32(plan, "plan"), max_tiles, _stream()), "moe_route")
 
 
 def moe_up(x: torch.Tensor, wgu: torch.Tensor, perm: torch.Tensor, offsets: torch.Tensor, plan: torch.Tensor,
-           max_tiles: int, top: int, act: str, out: torch.Tensor) -> None:
+           max_tiles: int, top: int, act: str, out: torch.Tensor, kernel: str = "auto") -> None:
     """out[i, :] = act(x[t] Wg[e]^T) * (x[t] Wu[e]^T) for sorted pair i (token t = perm[i] // top) of
-    expert e; wgu: [E, 2 * ff, K] with the gate rows first."""
+    expert e; wgu: [E, 2 * ff, K] with the gate rows first.  bfloat16 runs on the tensor cores where K
+    is a multiple of 8; kernel="generic" keeps the CUDA-core kernel."""
     e, ff2, k = wgu.shape
     assert x.shape[1] == k and out.shape[1] * 2 == ff2 and x.dtype == wgu.dtype == out.dtype
     _check(library().ems_moe_up(_ptr(x, "x"), _ptr(wgu, "wgu"), _dt(x), _i32(perm, "perm"), _i32(plan, "plan"),
-                                max_tiles, top, ff2 // 2, k, GLU_ACTIVATIONS[act], _ptr(out, "out"), _stream()),
-           "moe_up")
+                                max_tiles, top, ff2 // 2, k, GLU_ACTIVATIONS[act], _ptr(out, "out"),
+                                1 if kernel == "generic" else 0, _stream()), "moe_up")
 
 
 def moe_down(act: torch.Tensor, wdown: torch.Tensor, perm: torch.Tensor, offsets: torch.Tensor, plan: torch.Tensor,
-             max_tiles: int, y: torch.Tensor) -> None:
+             max_tiles: int, y: torch.Tensor, kernel: str = "auto") -> None:
     """y[perm[i], :] = act[i, :] Wd[e]^T (float32, in pair order) for sorted pair i of expert e;
     wdown: [E, H, ff]."""
     e, h, ff = wdown.shape
     assert act.shape[1] == ff and y.shape[1] == h and y.dtype == torch.float32 and act.dtype == wdown.dtype
     _check(library().ems_moe_down(_ptr(act, "act"), _ptr(wdown, "wdown"), _dt(act), _i32(perm, "perm"),
-                                  _i32(plan, "plan"), max_tiles, h, ff, _ptr(y, "y"), _stream()), "moe_down")
+                                  _i32(plan, "plan"), max_tiles, h, ff, _ptr(y, "y"),
+                                  1 if kernel == "generic" else 0, _stream()), "moe_down")
 
 
 def moe_combine(y: torch.Tensor, weights: torch.Tensor, out: torch.Tensor, top: int) -> None:

@@ -89,7 +89,7 @@ class RoutedGLU(FeedForward):
         max_tiles = K.moe_max_tiles(pairs, e, tile)
         ids = ctx.scratch("moe_ids", (pairs,), torch.int32)
         weights = ctx.scratch("moe_weights", (pairs,), torch.float32)
-        offsets = ctx.scratch("moe_offsets", (e + 1,), torch.int32)
+        offsets = ctx.scratch("moe_offsets", (3 * e + 1,), torch.int32)
         perm = ctx.scratch("moe_perm", (pairs,), torch.int32)
         plan = ctx.scratch("moe_plan", (1 + 3 * max_tiles,), torch.int32)
         K.moe_route(logits, top, s.renormalize, ids, weights, offsets, perm, plan, max_tiles)

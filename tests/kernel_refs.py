@@ -381,7 +381,7 @@ def moe_route(logits, top, renormalize, ids, weights, offsets, perm, plan, max_t
     offsets[1:e + 1] = torch.cumsum(counts, 0).to(torch.int32)
 
 
-def moe_up(x, wgu, perm, offsets, plan, max_tiles, top, act, out):
+def moe_up(x, wgu, perm, offsets, plan, max_tiles, top, act, out, kernel="auto"):
     e, ff2, k = wgu.shape
     ff = ff2 // 2
     off = offsets.tolist()
@@ -394,7 +394,7 @@ def moe_up(x, wgu, perm, offsets, plan, max_tiles, top, act, out):
         out[lo:hi] = (_glu_activation(y[:, :ff], act) * y[:, ff:]).to(out.dtype)
 
 
-def moe_down(act, wdown, perm, offsets, plan, max_tiles, y):
+def moe_down(act, wdown, perm, offsets, plan, max_tiles, y, kernel="auto"):
     e = wdown.shape[0]
     off = offsets.tolist()
     for ex in range(e):

@@ -250,7 +250,7 @@ def test_latent_attention_finds_a_planted_key(dtype):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
 @pytest.mark.parametrize("n,experts,top,ff,width", [(1, 4, 1, 16, 64), (37, 5, 2, 24, 48), (300, 3, 3, 8, 40),
-                                                    (130, 12, 3, 96, 256)])
+                                                    (130, 12, 3, 96, 256), (20, 3, 2, 12, 36), (700, 6, 2, 200, 136)])
 def test_routed_experts_against_plain(dtype, n, experts, top, ff, width):
     from emberserve_b200.parts.base import StepContext
     from emberserve_b200.parts.moe import RoutedGLU, RoutedGLUSpec
