@@ -20,75 +20,10 @@ namespace ems {
 
 constexpr int MOE_TM = 64, MOE_TN = 64, MOE_TK = 16;
 
-// plan (int32): [0] number of tiles; [1 .. 1 + 3 * max_tiles) expert, first sorted row and row
-// count of each tile.  One block.
-__global__ void moe_route_kernel(const float* __restrict__ logits, int n, int E, int top, int renorm,
-                                 int* __restrict__ ids, float* __restrict__ wts, int* __restrict__ offsets,
-                                 int* __restrict__ perm, int* __restrict__ plan, int max_tiles) {
-    extern __shared__ int sh[];
-    int* counts = sh;       // [E]
-    int* cursor = sh + E;   // [E]
-    int* offs = sh + 2 * E; // [E + 1]
-    for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
-    __syncthreads();
-    for (int t = threadIdx.x; t < n; t += blockDim.x) {
-        const float* z = logits + (size_t)t * E;
-        float mx = -INFINITY;
-        for (int e = 0; e < E; ++e) mx = fmaxf(mx, z[e]);
-        float sum = 0.f;
-        for (int e = 0; e < E; ++e) sum += expf(z[e] - mx);
-        float chosen_sum = 0.f;
-        for (int k = 0; k < top; ++k) {
-            int best = -1;
-            float bv = -INFINITY;
-            for (int e = 0; e < E; ++e) {
-                bool taken = false;
-                for (int j = 0; j < k; ++j) taken |= ids[(size_t)t * top + j] == e;
-                if (!taken && (best < 0 || z[e] > bv)) {
-                    best = e;
-                    bv = z[e];
-                }
-            }
-            ids[(size_t)t * top + k] = best;
-            const float s = expf(bv - mx) / sum;
-            wts[(size_t)t * top + k] = s;
-            chosen_sum += s;
-            atomicAdd(&counts[best], 1);
-        }
-        if (renorm)
-            for (int k = 0; k < top; ++k) wts[(size_t)t * top + k] /= chosen_sum;
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        int run = 0, nt = 0;
-        for (int e = 0; e < E; ++e) {
-            offs[e] = run;
-            offsets[e] = run;
-            cursor[e] = 0;
-            for (int r0 = 0; r0 < counts[e] && nt < max_tiles; r0 += MOE_TM, ++nt) {
-                plan[1 + 3 * nt] = e;
-                plan[2 + 3 * nt] = run + r0;
-                plan[3 + 3 * nt] = min(MOE_TM, counts[e] - r0);
-            }
-            run += counts[e];
-        }
-        offs[E] = run;
-        offsets[E] = run;
-        plan[0] = nt;
-    }
-    __syncthreads();
-    for (int t = threadIdx.x; t < n; t += blockDim.x)
-        for (int k = 0; k < top; ++k) {
-            const int e = ids[(size_t)t * top + k];
-            perm[offs[e] + atomicAdd(&cursor[e], 1)] = t * top + k;
-        }
-}
-
-// The same in three kernels for steps of many tokens: one thread per token chooses and counts
-// (counts in global memory, zeroed before), one block lays out offsets and tiles, one thread per
-// pair takes its place among its expert's rows.
-__device__ __forceinline__ void moe_choose(const float* __restrict__ z, int E, int top, int renorm,
-                                           int* __restrict__ ids, float* __restrict__ wts, int* counts) {
+// One warp chooses for one token: lane l holds the logits of experts l, l + 32, ... (up to 8 each,
+// so up to 256 experts; more are chosen by one lane alone).  Ties go to the lower index.
+__device__ __forceinline__ void moe_choose_serial(const float* __restrict__ z, int E, int top, int renorm,
+                                                  int* __restrict__ ids, float* __restrict__ wts, int* counts) {
     float mx = -INFINITY;
     for (int e = 0; e < E; ++e) mx = fmaxf(mx, z[e]);
     float sum = 0.f;
@@ -115,10 +50,110 @@ __device__ __forceinline__ void moe_choose(const float* __restrict__ z, int E, i
         for (int k = 0; k < top; ++k) wts[k] /= chosen_sum;
 }
 
+__device__ __forceinline__ void moe_choose_warp(const float* __restrict__ z, int E, int top, int renorm,
+                                                int* __restrict__ ids, float* __restrict__ wts, int* counts) {
+    const int lane = threadIdx.x & 31;
+    if (E > 256) {
+        if (lane == 0) moe_choose_serial(z, E, top, renorm, ids, wts, counts);
+        return;
+    }
+    float v[8];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int e = lane + 32 * i;
+        v[i] = e < E ? z[e] : -INFINITY;
+        mx = fmaxf(mx, v[i]);
+    }
+    mx = warp_max(mx);
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        if (lane + 32 * i < E) sum += expf(v[i] - mx);
+    sum = warp_sum(sum);
+    float chosen_sum = 0.f;
+    unsigned taken = 0u;  // bit i: my expert lane + 32 i is chosen already
+    for (int k = 0; k < top; ++k) {
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (lane + 32 * i < E && !((taken >> i) & 1u) && (bi == 0x7fffffff || v[i] > bv)) {
+                bv = v[i];
+                bi = lane + 32 * i;
+            }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) {
+                bv = ov;
+                bi = oi;
+            }
+        }
+        const float s = expf(bv - mx) / sum;
+        chosen_sum += s;
+        if (lane == 0) {
+            ids[k] = bi;
+            wts[k] = s;
+            atomicAdd(&counts[bi], 1);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (lane + 32 * i == bi) taken |= 1u << i;
+    }
+    __syncwarp();
+    if (renorm && lane == 0)
+        for (int k = 0; k < top; ++k) wts[k] /= chosen_sum;
+}
+
+// plan (int32): [0] number of tiles; [1 .. 1 + 3 * max_tiles) expert, first sorted row and row
+// count of each tile.  One block.
+__global__ void moe_route_kernel(const float* __restrict__ logits, int n, int E, int top, int renorm,
+                                 int* __restrict__ ids, float* __restrict__ wts, int* __restrict__ offsets,
+                                 int* __restrict__ perm, int* __restrict__ plan, int max_tiles) {
+    extern __shared__ int sh[];
+    int* counts = sh;       // [E]
+    int* cursor = sh + E;   // [E]
+    int* offs = sh + 2 * E; // [E + 1]
+    for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
+    __syncthreads();
+    for (int t = threadIdx.x >> 5; t < n; t += blockDim.x >> 5)
+        moe_choose_warp(logits + (size_t)t * E, E, top, renorm, ids + (size_t)t * top, wts + (size_t)t * top, counts);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0, nt = 0;
+        for (int e = 0; e < E; ++e) {
+            offs[e] = run;
+            offsets[e] = run;
+            cursor[e] = 0;
+            for (int r0 = 0; r0 < counts[e] && nt < max_tiles; r0 += MOE_TM, ++nt) {
+                plan[1 + 3 * nt] = e;
+                plan[2 + 3 * nt] = run + r0;
+                plan[3 + 3 * nt] = min(MOE_TM, counts[e] - r0);
+            }
+            run += counts[e];
+        }
+        offs[E] = run;
+        offsets[E] = run;
+        plan[0] = nt;
+    }
+    __syncthreads();
+    for (int t = threadIdx.x; t < n; t += blockDim.x)
+        for (int k = 0; k < top; ++k) {
+            const int e = ids[(size_t)t * top + k];
+            perm[offs[e] + atomicAdd(&cursor[e], 1)] = t * top + k;
+        }
+}
+
+// The same in three kernels for steps of many tokens: one warp per token chooses and counts
+// (counts in global memory, zeroed before), one block lays out offsets and tiles, one thread per
+// pair takes its place among its expert's rows.
 __global__ void moe_choose_kernel(const float* __restrict__ logits, int n, int E, int top, int renorm,
                                   int* __restrict__ ids, float* __restrict__ wts, int* __restrict__ counts) {
-    const int t = blockIdx.x * blockDim.x + threadIdx.x;
-    if (t < n) moe_choose(logits + (size_t)t * E, E, top, renorm, ids + (size_t)t * top, wts + (size_t)t * top, counts);
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t < n)
+        moe_choose_warp(logits + (size_t)t * E, E, top, renorm, ids + (size_t)t * top, wts + (size_t)t * top, counts);
 }
 
 // offsets: [E + 1]; counts and cursor: [E] each (the cursors are set to zero here)
@@ -238,11 +273,12 @@ moe_grouped_kernel(const T* __restrict__ a, const T* __restrict__ w, const int* 
 // ---------------------------------------------------------------------------------------
 // The same two products on the tensor cores (bfloat16, mma.sync m16n8k16, float32 accumulators).
 // A block computes 64 sorted rows x 128 weight rows through a three-stage cp.async ring of
-// 32-column slices; the activations' rows are gathered through the pair list as they are copied.
+// 64-column slices; the activations' rows are gathered through the pair list as they are copied.
 // GLU: the 128 weight rows are 64 gate rows and the 64 up rows of the same outputs, and a warp
 // holds both halves of its outputs, so the activation is applied in registers.
 
-constexpr int MM_TM = 64, MM_TB = 128, MM_TK = 32, MM_PAD = 8, MM_STAGES = 3;
+constexpr int MM_TM = 64, MM_TB = 128, MM_TK = 64, MM_PAD = 8, MM_STAGES = 3;
+constexpr int MM_SMEM = MM_STAGES * (MM_TM + MM_TB) * (MM_TK + MM_PAD) * 2;  // bytes of the ring
 
 __device__ __forceinline__ void mm_cp_async16(uint32_t dst, const void* src, bool valid) {
     const int bytes = valid ? 16 : 0;
@@ -266,8 +302,9 @@ moe_grouped_mma_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, c
                        const int* __restrict__ plan, int top, int N, int K, int act, bf16* __restrict__ out_t,
                        float* __restrict__ out_f) {
     constexpr int LDS = MM_TK + MM_PAD;  // elements per shared-memory row
-    __shared__ __align__(16) bf16 As[MM_STAGES][MM_TM][LDS];
-    __shared__ __align__(16) bf16 Bs[MM_STAGES][MM_TB][LDS];
+    extern __shared__ __align__(16) unsigned char mm_smem[];
+    bf16* As = reinterpret_cast<bf16*>(mm_smem);      // [MM_STAGES][MM_TM][LDS]
+    bf16* Bs = As + MM_STAGES * MM_TM * LDS;          // [MM_STAGES][MM_TB][LDS]
     __shared__ int src_row[MM_TM];
     const int tile = blockIdx.x;
     if (tile >= plan[0]) return;
@@ -280,23 +317,25 @@ moe_grouped_mma_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, c
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int wm = warp >> 2, wn = warp & 3;  // 2 x 4 warps: 32 rows x (GLU ? 16 + 16 : 32) weight rows each
-    const uint32_t as_base = (uint32_t)__cvta_generic_to_shared(&As[0][0][0]);
-    const uint32_t bs_base = (uint32_t)__cvta_generic_to_shared(&Bs[0][0][0]);
+    const uint32_t as_base = (uint32_t)__cvta_generic_to_shared(As);
+    const uint32_t bs_base = (uint32_t)__cvta_generic_to_shared(Bs);
     const int ktiles = (K + MM_TK - 1) / MM_TK;
 
     auto load = [&](int kt, int stage) {
         const int k0 = kt * MM_TK;
-        {   // activations: 64 rows x 4 chunks, one per thread
-            const int r = threadIdx.x >> 2, c = (threadIdx.x & 3) * 8;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {  // activations: 64 rows x 8 chunks of 16 bytes
+            const int idx = threadIdx.x + i * 256;
+            const int r = idx >> 3, c = (idx & 7) * 8;
             const int ar = src_row[r];
             const bool ok = ar >= 0 && k0 + c < K;
             mm_cp_async16(as_base + (uint32_t)(((stage * MM_TM + r) * LDS + c) * 2),
                           ok ? a + (size_t)ar * K + k0 + c : a, ok);
         }
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {  // weights: 128 rows x 4 chunks
+        for (int i = 0; i < 4; ++i) {  // weights: 128 rows x 8 chunks
             const int idx = threadIdx.x + i * 256;
-            const int r = idx >> 2, c = (idx & 3) * 8;
+            const int r = idx >> 3, c = (idx & 7) * 8;
             int nn;  // the weight row that lands in shared row r
             if (GLU) nn = r < NOUT ? n0 + r : N + n0 + (r - NOUT);
             else nn = n0 + r;
@@ -409,13 +448,12 @@ EMS_EXPORT int ems_moe_route(const float* logits, int n, int E, int top, int ren
         int* counts = offsets + E + 1;
         int* cursor = counts + E;
         if (cudaMemsetAsync(counts, 0, (size_t)E * sizeof(int), stream) != cudaSuccess) return EMS_ERR_LAUNCH;
-        moe_choose_kernel<<<(n + 127) / 128, 128, 0, stream>>>(logits, n, E, top, renorm, ids, wts, counts);
+        moe_choose_kernel<<<(n + 7) / 8, 256, 0, stream>>>(logits, n, E, top, renorm, ids, wts, counts);
         moe_plan_kernel<<<1, 32, 0, stream>>>(E, counts, cursor, offsets, plan, max_tiles);
         moe_scatter_kernel<<<(n * top + 255) / 256, 256, 0, stream>>>(ids, n * top, offsets, cursor, perm);
         return launch_status();
     }
-    int th = 32;
-    while (th < n && th < 1024) th <<= 1;
+    int th = 32 * (n < 32 ? n : 32);  // a warp per token, up to 32 warps
     moe_route_kernel<<<1, th, smem, stream>>>(logits, n, E, top, renorm, ids, wts, offsets, perm, plan, max_tiles);
     return launch_status();
 }
@@ -426,7 +464,8 @@ EMS_EXPORT int ems_moe_up(const void* x, const void* wgu, int dtype, const int* 
     // impl: 0 the tensor-core kernel where it takes the case, 1 always the CUDA-core kernel
     if (dtype == EMS_BF16 && impl == 0 && moe_mma_ok(x, wgu, K)) {
         dim3 mg(max_tiles, (ff + MM_TB / 2 - 1) / (MM_TB / 2));
-        moe_grouped_mma_kernel<true><<<mg, 256, 0, stream>>>((const bf16*)x, (const bf16*)wgu, perm, plan, top, ff, K,
+        cudaFuncSetAttribute(moe_grouped_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, MM_SMEM);
+        moe_grouped_mma_kernel<true><<<mg, 256, MM_SMEM, stream>>>((const bf16*)x, (const bf16*)wgu, perm, plan, top, ff, K,
                                                              act, (bf16*)out, nullptr);
         return launch_status();
     }
@@ -447,7 +486,8 @@ EMS_EXPORT int ems_moe_down(const void* a, const void* wdown, int dtype, const i
     if (max_tiles <= 0) return EMS_OK;
     if (dtype == EMS_BF16 && impl == 0 && moe_mma_ok(a, wdown, ff)) {
         dim3 mg(max_tiles, (H + MM_TB - 1) / MM_TB);
-        moe_grouped_mma_kernel<false><<<mg, 256, 0, stream>>>((const bf16*)a, (const bf16*)wdown, perm, plan, 1, H, ff,
+        cudaFuncSetAttribute(moe_grouped_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, MM_SMEM);
+        moe_grouped_mma_kernel<false><<<mg, 256, MM_SMEM, stream>>>((const bf16*)a, (const bf16*)wdown, perm, plan, 1, H, ff,
                                                               0, nullptr, y);
         return launch_status();
     }

@@ -197,10 +197,11 @@ def _run_latent(case, heads, r, p, scale, splits=1, kernel="auto"):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
 @pytest.mark.parametrize("heads,r,p", [(3, 24, 8), (1, 40, 6), (10, 160, 2), (8, 96, 32), (5, 320, 0), (2, 16, 64),
-                                       (16, 512, 64), (20, 128, 16), (1, 32, 16)])
+                                       (16, 512, 64), (20, 128, 16), (1, 32, 16), (4, 256, 16)])
 def test_latent_attention_kernel_against_dense(dtype, heads, r, p):
     """Both kernels: the generic one (every geometry, both types) and the tensor-core one, which
-    bfloat16 takes where the sizes allow (here the last four geometries and (8, 96, 32))."""
+    bfloat16 takes where the sizes allow (here the last five geometries and (8, 96, 32)), with four
+    warps or, for long latents, eight."""
     scale = 0.3 / math.sqrt(r + p)
     case = _latent_case(r + heads, dtype, heads, r, p, ctx_lens=[70, 1, 33, 200], q_lens=[70, 1, 2, 1], page_size=16)
     want = _latent_dense(case, heads, r, p, scale)
@@ -293,6 +294,44 @@ def test_routed_experts_against_plain(dtype, n, experts, top, ff, width):
             num_tokens=1, num_rows=1, dtype=dtype, device=torch.device(DEV), tokens=None, positions=None,
             row_of_token=None, cu_q=None, starts=None, q_lens=[1], start_list=[0], scratch=scratch)).cpu().double()
         assert (one[0] - got[5]).abs().max() <= 1e-6 * want.abs().max() + (0 if dtype == torch.float32 else 1e-2)
+
+
+@pytest.mark.parametrize("n,experts,top", [(5, 3, 3), (70, 40, 5), (900, 64, 6), (33, 300, 4), (600, 9, 1)])
+def test_routing_alone(n, experts, top):
+    """Scores, choice (ties to the lower index), weights with and without renormalisation, and the
+    sorted layout: every pair appears once, among the rows of its expert."""
+    K = _K()
+    g = torch.Generator().manual_seed(n)
+    logits = torch.randn(n, experts, generator=g) * 3
+    logits[0, :] = 1.5  # all equal: the first `top` experts win
+    if experts > 4:
+        logits[1, 2] = logits[1, 4] = 9.0  # two equal maxima
+    tile = K.moe_tile_rows()
+    max_tiles = K.moe_max_tiles(n * top, experts, tile)
+    for renorm in (False, True):
+        ids = torch.empty(n * top, dtype=torch.int32, device=DEV)
+        wts = torch.empty(n * top, device=DEV)
+        offsets = torch.empty(3 * experts + 1, dtype=torch.int32, device=DEV)
+        perm = torch.full((n * top,), -1, dtype=torch.int32, device=DEV)
+        plan = torch.empty(1 + 3 * max_tiles, dtype=torch.int32, device=DEV)
+        K.moe_route(logits.to(DEV), top, renorm, ids, wts, offsets, perm, plan, max_tiles)
+        s = torch.softmax(logits.double(), -1)
+        order = torch.argsort(-logits.double(), dim=-1, stable=True)[:, :top]
+        assert torch.equal(ids.cpu().view(n, top).long(), order)
+        want = torch.gather(s, 1, order)
+        if renorm:
+            want = want / want.sum(-1, keepdim=True)
+        assert (wts.cpu().view(n, top).double() - want).abs().max() < 1e-6
+        off = offsets.cpu()[:experts + 1].tolist()
+        assert off[0] == 0 and off[-1] == n * top
+        p = perm.cpu().long()
+        assert sorted(p.tolist()) == list(range(n * top))
+        flat = ids.cpu().long()
+        for e in range(experts):
+            assert bool((flat[p[off[e]:off[e + 1]]] == e).all())
+        pl = plan.cpu().tolist()
+        covered = sum(pl[3 + 3 * i] for i in range(pl[0]))
+        assert covered == n * top and all(pl[3 + 3 * i] <= tile for i in range(pl[0]))
 
 
 @pytest.mark.parametrize("act", ["relu", "silu", "gelu_tanh"])
