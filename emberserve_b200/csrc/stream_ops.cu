@@ -102,6 +102,132 @@ __global__ void add_norm_grouped_kernel(const T* __restrict__ delta, const void*
         o[i] = from_f32<T>(buf[i] * stat[i / gs] * load_any(gain, g_dtype, i));
 }
 
+
+// The same with four columns per thread held in registers between the phases (H and the group
+// sizes multiples of 4, H <= 4 * VPT * blockDim): a row is one round trip to memory.
+template <typename T> struct Vec4s;
+template <> struct Vec4s<float> {
+    static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+        const float4 t = *reinterpret_cast<const float4*>(p);
+        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float (&v)[4]) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+};
+template <> struct Vec4s<bf16> {
+    static __device__ __forceinline__ void load(const bf16* p, float (&v)[4]) {
+        const uint2 t = *reinterpret_cast<const uint2*>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.y));
+        v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+    }
+    static __device__ __forceinline__ void store(bf16* p, const float (&v)[4]) {
+        const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+        uint2 t;
+        t.x = *reinterpret_cast<const uint32_t*>(&a);
+        t.y = *reinterpret_cast<const uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = t;
+    }
+};
+
+__device__ __forceinline__ void load_gain4(const void* w, int dtype, int col, float (&v)[4]) {
+    if (dtype == EMS_F32) Vec4s<float>::load(reinterpret_cast<const float*>(w) + col, v);
+    else Vec4s<bf16>::load(reinterpret_cast<const bf16*>(w) + col, v);
+}
+
+// Per-group factors 1 / sqrt(mean + eps) from each thread's share `ss[v]` of the sum of squares of
+// its chunk v (whose group is grp[v]); left in stat[0 .. groups).
+template <int VPT>
+__device__ __forceinline__ void group_factors(const float (&ss)[VPT], const int (&grp)[VPT], int groups, int gs,
+                                              float eps, float* stat, float* red) {
+    for (int g = 0; g < groups; ++g) {
+        float mine = 0.f;
+#pragma unroll
+        for (int v = 0; v < VPT; ++v)
+            if (grp[v] == g) mine += ss[v];
+        const float total = block_sum(mine, red);
+        if (threadIdx.x == 0) stat[g] = 1.0f / sqrtf(total / (float)gs + eps);
+    }
+    __syncthreads();
+}
+
+template <typename T, int VPT>
+__global__ void add_norm_grouped_vec_kernel(const T* __restrict__ delta, const void* __restrict__ post_gain,
+                                            int pg_dtype, int post_groups, float post_eps, float* residual,
+                                            const void* __restrict__ gain, int g_dtype, int groups, float eps,
+                                            T* __restrict__ out, const int* __restrict__ rows, int H,
+                                            int write_residual) {
+    __shared__ float red[33];
+    __shared__ float stat[64], stat2[64];
+    const size_t r = blockIdx.x;
+    const size_t src = rows ? (size_t)rows[r] : r;
+    float* res = residual + src * H;
+    const T* dl = delta ? delta + src * H : nullptr;
+    float x[VPT][4], ss[VPT];
+    int grp[VPT];
+    const int gs_post = post_gain ? H / post_groups : H, gs = H / groups;
+    if (dl && post_gain) {
+#pragma unroll
+        for (int v = 0; v < VPT; ++v) {
+            const int col = (v * blockDim.x + threadIdx.x) * 4;
+            ss[v] = 0.f;
+            grp[v] = -1;
+            if (col < H) {
+                Vec4s<T>::load(dl + col, x[v]);
+                grp[v] = col / gs_post;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) ss[v] += x[v][i] * x[v][i];
+            }
+        }
+        group_factors<VPT>(ss, grp, post_groups, gs_post, post_eps, stat, red);
+    }
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+        const int col = (v * blockDim.x + threadIdx.x) * 4;
+        ss[v] = 0.f;
+        if (col < H) {
+            float rr[4];
+            Vec4s<float>::load(res + col, rr);
+            if (dl && post_gain) {
+                float w[4];
+                load_gain4(post_gain, pg_dtype, col, w);
+                const float f = stat[grp[v]];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) rr[i] += x[v][i] * f * w[i];
+            } else if (dl) {
+                float d[4];
+                Vec4s<T>::load(dl + col, d);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) rr[i] += d[i];
+            }
+            if (dl && write_residual) Vec4s<float>::store(res + col, rr);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                x[v][i] = rr[i];
+                ss[v] += rr[i] * rr[i];
+            }
+            grp[v] = col / gs;
+        } else {
+            grp[v] = -1;
+        }
+    }
+    group_factors<VPT>(ss, grp, groups, gs, eps, stat2, red);
+    T* o = out + r * H;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+        const int col = (v * blockDim.x + threadIdx.x) * 4;
+        if (col < H) {
+            float w[4], y[4];
+            load_gain4(gain, g_dtype, col, w);
+            const float f = stat2[grp[v]];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) y[i] = x[v][i] * f * w[i];
+            Vec4s<T>::store(o + col, y);
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------
 // out[n, i] = act(gu[n, i]) * gu[n, I + i];  act: 0 SiLU, 1 ReLU, 2 GELU (tanh form)
 
@@ -221,6 +347,33 @@ EMS_EXPORT int ems_add_norm_grouped(const void* delta, const void* post_gain, in
     if (n <= 0) return EMS_OK;
     if (groups <= 0 || H % groups || (post_gain && (post_groups <= 0 || H % post_groups))) return EMS_ERR_SHAPE;
     const int most = groups > post_groups ? groups : post_groups;
+    // four columns per thread in registers where the sizes allow: one trip to memory per row
+    const bool aligned = !(reinterpret_cast<uintptr_t>(delta) & 15) && !(reinterpret_cast<uintptr_t>(residual) & 15) &&
+                         !(reinterpret_cast<uintptr_t>(out) & 15) && !(reinterpret_cast<uintptr_t>(gain) & 15) &&
+                         !(reinterpret_cast<uintptr_t>(post_gain) & 15);
+    if (aligned && H % 4 == 0 && (H / groups) % 4 == 0 && (!post_gain || (H / post_groups) % 4 == 0) && most <= 64 &&
+        H <= 4 * 8 * 256) {
+        int th = 32;
+        while (th < 256 && th * 4 < H) th <<= 1;
+        const int vpt = (H + 4 * th - 1) / (4 * th);
+#define EMS_LAUNCH_NORM_VEC(T, V)                                                                              \
+    add_norm_grouped_vec_kernel<T, V><<<n, th, 0, stream>>>((const T*)delta, post_gain, pg_dtype, post_groups, \
+                                                            post_eps, (float*)residual, gain, g_dtype, groups, \
+                                                            eps, (T*)out, rows, H, write_residual)
+#define EMS_NORM_VEC_BY_VPT(T)                         \
+    do {                                               \
+        if (vpt <= 1) EMS_LAUNCH_NORM_VEC(T, 1);       \
+        else if (vpt <= 2) EMS_LAUNCH_NORM_VEC(T, 2);  \
+        else if (vpt <= 4) EMS_LAUNCH_NORM_VEC(T, 4);  \
+        else EMS_LAUNCH_NORM_VEC(T, 8);                \
+    } while (0)
+        if (dtype == EMS_F32) EMS_NORM_VEC_BY_VPT(float);
+        else if (dtype == EMS_BF16) EMS_NORM_VEC_BY_VPT(bf16);
+        else return EMS_ERR_DTYPE;
+#undef EMS_NORM_VEC_BY_VPT
+#undef EMS_LAUNCH_NORM_VEC
+        return launch_status();
+    }
     const size_t smem = (size_t)(H + most) * sizeof(float);
     if (smem > 200 * 1024) return EMS_ERR_SHAPE;
     const int th = threads_for(H);
