@@ -34,7 +34,9 @@ from emberserve_b200.parts.base import (Mixer, PagedLatent, PagedLatentHandle, P
 from emberserve_b200.parts.linear import linear
 
 # Keys of a token are cut over several blocks when a step has too few tokens to fill the device.
-_BLOCKS_PER_SM = 2
+# One block per SM is the aim: at real sizes (512 + 64 numbers per key) a block's two tiles of keys
+# take most of an SM's shared memory (64 rows at 2048 keys: 73 us with 128 blocks, 81 with 256).
+_BLOCKS_PER_SM = 1
 _MAX_SPLITS = 64
 _MIN_KEYS_PER_SPLIT = 128
 
@@ -151,7 +153,8 @@ class LatentAttention(Mixer):
         torch.bmm(q.view(n, h, self.q_head)[:, :, :s.nope_dim].transpose(0, 1),
                   self.wuk.view(h, s.nope_dim, r), out=qlat)
         olat = ctx.scratch("lat_olat", (h, n, r), ctx.dtype)
-        chunks = -(-h // 8)
+        # (a block of the tensor-core kernel serves 16 heads, one of the generic kernel 8)
+        chunks = -(-h // (16 if ctx.dtype == torch.bfloat16 else 8))
         splits = latent_splits(n, chunks, ctx.max_ctx_len, K.sm_count(ctx.device))
         scratch = None
         if splits > 1:
