@@ -492,3 +492,26 @@ def test_greedy_generation_through_the_entry_point(dam_dirs, name):
         assert got == want, how
         st = llm.engine.runner.cache.stats()
         assert st.num_free == st.num_pages and st.free_state_slots == st.num_state_slots
+
+
+def test_command_line_random_weights_then_generate(tmp_path):
+    """`random-weights` writes a Damolorn folder from its config.json; `generate` on it prints the
+    tokens that LLM.generate returns (sampled with a seed, bfloat16)."""
+    from emberserve_b200 import LLM, SamplingParams
+
+    (tmp_path / "config.json").write_text(json.dumps(td.DAM_A))
+    model = tmp_path / "model"
+    proc = subprocess.run([sys.executable, "-m", "emberserve_b200", "random-weights", "--config",
+                           str(tmp_path / "config.json"), "--out", str(model), "--seed", "5", "--std", "0.3"],
+                          capture_output=True, text=True, cwd=ROOT, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-1500:]
+    prompt = [7, 50, 33, 90, 9]
+    llm = LLM(str(model), dtype="bfloat16", device=DEV, block_size=16, num_gpu_blocks=64, max_model_len=200)
+    want = llm.generate([prompt], SamplingParams(max_tokens=6, temperature=0.7, top_k=20, seed=11))[0]
+    proc = subprocess.run(
+        [sys.executable, "-m", "emberserve_b200", "generate", "--model", str(model), "--dtype", "bfloat16",
+         "--block-size", "16", "--num-blocks", "64", "--max-model-len", "200", "--prompt-ids",
+         ",".join(map(str, prompt)), "--max-tokens", "6", "--temperature", "0.7", "--top-k", "20", "--seed", "11"],
+        capture_output=True, text=True, cwd=ROOT, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-1500:]
+    assert [int(t) for t in proc.stdout.split()] == want.output_token_ids

@@ -132,3 +132,21 @@ def test_every_layer_run_has_cache_entries_of_its_own():
     assert sorted(ids) == list(range(2 * runs))
     dec = build_decoder(td.typed(td.DAM_C))  # one tap: nothing but the pages to keep
     assert all(isinstance(call.cache, int) for call in dec.spec.order)
+
+
+def test_random_weights_folder_loads_and_steps(tmp_path):
+    """The random-weights mode writes every tensor the design names (norm gains as ones), and the
+    folder loads through the registry and runs a step."""
+    from emberserve_b200.engine.runner import StepRow
+    from emberserve_b200.weights.loader import write_random_model
+
+    cfg = td.typed(td.DAM_C)
+    out = write_random_model(cfg, tmp_path / "m", seed=3, std=0.2)
+    _, w = plain.read_model_dir(out)
+    assert set(w) == set(td.tensor_shapes(td.DAM_C))
+    assert bool((w["l0.norm1"] == 1).all()) and bool((w["final.norm"] == 1).all())
+    runner = host_runner(out, page_size=8, num_pages=8, num_state_slots=2)
+    runner.cache.admit(0, 5)
+    logits = runner.step([StepRow(0, [1, 2, 3, 4, 5], 0, [4])])
+    want = plain.forward(td.DAM_C, w, [1, 2, 3, 4, 5], torch.float64)[-1]
+    assert (logits[0].double() - want).abs().max() < 1e-4 * want.abs().max()
