@@ -51,6 +51,12 @@ struct GemmLargeParams {
     int m_tiles;        // of 256 token rows
     int n_tiles;        // GATED: of 128 outputs; else of 256
     int tiled;          // the weight map is that of the tiled copy (tc_weight_map)
+    // Grouped form (routed experts): row tile m of x belongs to expert tile_expert[m] (-1: the tile
+    // is not in use and is skipped by every role), whose weight rows start at expert * expert_rows.
+    // The table is written by the kernel before this one, so nothing is requested before the
+    // dependency wait.  nullptr: one weight for all rows.
+    const int* tile_expert = nullptr;
+    int expert_rows = 0;
 };
 
 __device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, uint32_t rank) {
@@ -183,8 +189,8 @@ gemm_large_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
         // The weights do not depend on the kernel before this one (the launch is a programmatic
         // dependent): the weight halves of the first stages are requested at once, the token rows
         // after the dependency wait.
-        const int pre = pair < total ? min(p.k_tiles, GL_STAGES) : 0;
-        {
+        const int pre = (pair < total && !p.tile_expert) ? min(p.k_tiles, GL_STAGES) : 0;
+        if (pre > 0) {
             const int n_tile = pair / p.m_tiles;
             const int w_row = GATED ? (int)rank * p.n_out + n_tile * GL_BN : n_tile * 2 * GL_BN + (int)rank * GL_BN;
             for (int kb = 0; kb < pre; ++kb) {
@@ -195,8 +201,11 @@ gemm_large_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
         grid_dependency_wait();
         for (int tile = pair; tile < total && ok; tile += pairs) {
             const int n_tile = tile / p.m_tiles, m_tile = tile % p.m_tiles;
+            const int expert = p.tile_expert ? p.tile_expert[m_tile] : 0;
+            if (expert < 0) continue;
             const int x_row = m_tile * 2 * GL_BM + (int)rank * GL_BM;
-            const int w_row = GATED ? (int)rank * p.n_out + n_tile * GL_BN : n_tile * 2 * GL_BN + (int)rank * GL_BN;
+            const int w_row = expert * p.expert_rows +
+                              (GATED ? (int)rank * p.n_out + n_tile * GL_BN : n_tile * 2 * GL_BN + (int)rank * GL_BN);
             for (int kb = 0; kb < p.k_tiles; ++kb, ++it) {
                 const int s = it % GL_STAGES;
                 const uint32_t dst = base + s * GL_STAGE_BYTES;
@@ -218,9 +227,11 @@ gemm_large_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
         // ---- MMA issue (leading block only): the warp runs the loop, one elected lane issues ---
         const bool issuer = elect_one();
         const uint32_t peer_empty0 = map_to_rank(empty0, 1), peer_tfull0 = map_to_rank(tfull0, 1);
+        if (p.tile_expert) grid_dependency_wait();  // the table of the grouped form comes from earlier kernels
         bool ok = true;
         int it = 0, si = 0;
-        for (int tile = pair; tile < total && ok; tile += pairs, ++si) {
+        for (int tile = pair; tile < total && ok; tile += pairs) {
+            if (p.tile_expert && p.tile_expert[tile % p.m_tiles] < 0) continue;
             const int b = si & 1;
             const uint32_t tph = (uint32_t)(si >> 1) & 1u;
             // both blocks have drained this accumulator
@@ -251,6 +262,7 @@ gemm_large_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
                 tc_commit_pair(peer_tfull0 + 8 * b);
             }
             __syncwarp();
+            ++si;
         }
     } else if (warp >= 2) {
         // ---- epilogue: eight warps; a warp reads the 32 token lanes of its quarter of tensor memory
@@ -265,8 +277,10 @@ gemm_large_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
         const int c_begin = half * SPAN, c_end = c_begin + SPAN;
         bool ok = true;
         int si = 0;
-        for (int tile = pair; tile < total && ok; tile += pairs, ++si) {
+        if (p.tile_expert) grid_dependency_wait();
+        for (int tile = pair; tile < total && ok; tile += pairs) {
             const int n_tile = tile / p.m_tiles, m_tile = tile % p.m_tiles;
+            if (p.tile_expert && p.tile_expert[m_tile] < 0) continue;
             const int b = si & 1;
             const uint32_t tph = (uint32_t)(si >> 1) & 1u;
             // one lane waits for the accumulator and tells the eight warps
@@ -291,6 +305,7 @@ gemm_large_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(lead_tempty0 + 8 * b);
+            ++si;
         }
     }
     __syncwarp();  // the lanes that had no role wait here for the one that had
@@ -377,5 +392,30 @@ EMS_EXPORT int ems_gemm_large_gated(const void* x, const void* w, void* act, int
     p.y = reinterpret_cast<bf16*>(act); p.bias = nullptr; p.status = status_dev; p.m_tok = m_tok; p.n_out = inter;
     p.k_tiles = (k + GL_BK - 1) / GL_BK; p.m_tiles = (m_tok + 2 * GL_BM - 1) / (2 * GL_BM); p.n_tiles = inter / GL_BN;
     p.tiled = tiled ? 1 : 0;
+    return launch_gemm_large<true>(mx, mw, p, stream);
+}
+
+// The gate/up product of routed experts in its grouped form: xs [rows, k] holds the (token, choice)
+// pairs sorted by expert, every expert's rows starting at a multiple of 256; tile_expert[m] names the
+// expert of row tile m (-1: not in use); w: [experts, 2 * inter, k].  act[rows, inter] =
+// silu(gate) * up for the rows of tiles in use.  inter a multiple of 128, k a multiple of 8.
+EMS_EXPORT int ems_moe_up_grouped_tc05(const void* xs, const void* w, void* act, int rows, int inter, int k,
+                                       int experts, const int* tile_expert, cudaStream_t stream) {
+    if (rows <= 0 || inter <= 0) return EMS_OK;
+    if (rows % (2 * GL_BM) || !ems_gemm_large_gated_supported(rows, inter, k) || experts <= 0) return EMS_ERR_SHAPE;
+    if (((uintptr_t)xs % 16) || ((uintptr_t)w % 16) || ((uintptr_t)act % 16)) return EMS_ERR_ALIGN;
+    int* status = tc_status_device_ptr();
+    if (!status) return EMS_ERR_LAUNCH;
+    int* status_dev = nullptr;
+    if (cudaHostGetDevicePointer(reinterpret_cast<void**>(&status_dev), status, 0) != cudaSuccess) return EMS_ERR_LAUNCH;
+    CUtensorMap mx, mw;
+    if (!tc_tensor_map_2d(xs, rows, k, GL_BM, &mx) || !tc_weight_map(w, 2LL * inter * experts, k, false, &mw))
+        return EMS_ERR_LAUNCH;
+    GemmLargeParams p;
+    p.y = reinterpret_cast<bf16*>(act); p.bias = nullptr; p.status = status_dev; p.m_tok = rows; p.n_out = inter;
+    p.k_tiles = (k + GL_BK - 1) / GL_BK; p.m_tiles = rows / (2 * GL_BM); p.n_tiles = inter / GL_BN;
+    p.tiled = 0;
+    p.tile_expert = tile_expert;
+    p.expert_rows = 2 * inter;
     return launch_gemm_large<true>(mx, mw, p, stream);
 }

@@ -156,14 +156,20 @@ __global__ void moe_choose_kernel(const float* __restrict__ logits, int n, int E
         moe_choose_warp(logits + (size_t)t * E, E, top, renorm, ids + (size_t)t * top, wts + (size_t)t * top, counts);
 }
 
-// offsets: [E + 1]; counts and cursor: [E] each (the cursors are set to zero here)
+// offsets: [E + 1]; counts and cursor: [E] each (the cursors are set to zero here).  With align > 1
+// every expert's rows start at a multiple of `align` (the rows between are nobody's), and big[m]
+// names the expert of the m-th group of `align` rows, -1 where the group is not in use.
 __global__ void moe_plan_kernel(int E, const int* __restrict__ counts, int* __restrict__ cursor,
-                                int* __restrict__ offsets, int* __restrict__ plan, int max_tiles) {
+                                int* __restrict__ offsets, int* __restrict__ plan, int max_tiles, int align,
+                                int* __restrict__ big, int max_big) {
     if (threadIdx.x != 0) return;
-    int run = 0, nt = 0;
+    int run = 0, nt = 0, nb = 0;
     for (int e = 0; e < E; ++e) {
+        if (align > 1) run = (run + align - 1) / align * align;
         offsets[e] = run;
         cursor[e] = 0;
+        if (big)
+            for (int r0 = 0; r0 < counts[e] && nb < max_big; r0 += align) big[nb++] = e;
         for (int r0 = 0; r0 < counts[e] && nt < max_tiles; r0 += MOE_TM, ++nt) {
             plan[1 + 3 * nt] = e;
             plan[2 + 3 * nt] = run + r0;
@@ -173,6 +179,20 @@ __global__ void moe_plan_kernel(int E, const int* __restrict__ counts, int* __re
     }
     offsets[E] = run;
     plan[0] = nt;
+    if (big)
+        for (; nb < max_big; ++nb) big[nb] = -1;
+}
+
+// xs[i, :] = x[perm[i] / top, :] for the sorted rows i that belong to a pair (perm[i] >= 0); K a
+// multiple of 8, 16-byte aligned rows.
+__global__ void moe_gather_kernel(const bf16* __restrict__ x, const int* __restrict__ perm, int top, int K,
+                                  bf16* __restrict__ xs) {
+    const int i = blockIdx.x;
+    const int p = perm[i];
+    if (p < 0) return;
+    const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(p / top) * K);
+    uint4* dst = reinterpret_cast<uint4*>(xs + (size_t)i * K);
+    for (int c = threadIdx.x; c < K / 8; c += blockDim.x) dst[c] = src[c];
 }
 
 __global__ void moe_scatter_kernel(const int* __restrict__ ids, int pairs, const int* __restrict__ offsets,
@@ -438,10 +458,16 @@ using namespace ems;
 
 EMS_EXPORT int ems_moe_tile_rows() { return MOE_TM; }
 
+// align > 1 (steps of more than 512 tokens only): every expert's sorted rows start at a multiple of
+// `align`; perm (max_big * align entries) holds -1 for the rows between, and big[0 .. max_big) names
+// the expert of every group of `align` rows (-1: not in use).
 EMS_EXPORT int ems_moe_route(const float* logits, int n, int E, int top, int renorm, int* ids, float* wts,
-                             int* offsets, int* perm, int* plan, int max_tiles, cudaStream_t stream) {
+                             int* offsets, int* perm, int* plan, int max_tiles, int align, int* big, int max_big,
+                             cudaStream_t stream) {
     if (n <= 0) return EMS_OK;
     if (top < 1 || top > E) return EMS_ERR_SHAPE;
+    if (align < 1 || (align > 1 && (n <= 512 || !big || max_big < n * top / align + (E < n * top ? E : n * top))))
+        return EMS_ERR_SHAPE;
     const size_t smem = (size_t)(3 * E + 1) * sizeof(int);
     if (smem > 48 * 1024) return EMS_ERR_SHAPE;
     if (n > 512) {  // `offsets` holds [offsets (E + 1) | counts (E) | cursors (E)]
@@ -449,7 +475,11 @@ EMS_EXPORT int ems_moe_route(const float* logits, int n, int E, int top, int ren
         int* cursor = counts + E;
         if (cudaMemsetAsync(counts, 0, (size_t)E * sizeof(int), stream) != cudaSuccess) return EMS_ERR_LAUNCH;
         moe_choose_kernel<<<(n + 7) / 8, 256, 0, stream>>>(logits, n, E, top, renorm, ids, wts, counts);
-        moe_plan_kernel<<<1, 32, 0, stream>>>(E, counts, cursor, offsets, plan, max_tiles);
+        if (align > 1 &&
+            cudaMemsetAsync(perm, 0xFF, (size_t)max_big * align * sizeof(int), stream) != cudaSuccess)
+            return EMS_ERR_LAUNCH;
+        moe_plan_kernel<<<1, 32, 0, stream>>>(E, counts, cursor, offsets, plan, max_tiles, align,
+                                              align > 1 ? big : nullptr, max_big);
         moe_scatter_kernel<<<(n * top + 255) / 256, 256, 0, stream>>>(ids, n * top, offsets, cursor, perm);
         return launch_status();
     }
@@ -500,6 +530,16 @@ EMS_EXPORT int ems_moe_down(const void* a, const void* wdown, int dtype, const i
                                                                   H, ff, 0, nullptr, y);
     else
         return EMS_ERR_DTYPE;
+    return launch_status();
+}
+
+EMS_EXPORT int ems_moe_gather(const void* x, const int* perm, int rows, int top, int K, void* xs,
+                              cudaStream_t stream) {
+    if (rows <= 0) return EMS_OK;
+    if (K % 8 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(xs) & 15)) return EMS_ERR_ALIGN;
+    int th = 32;
+    while (th < K / 8 && th < 256) th <<= 1;
+    moe_gather_kernel<<<rows, th, 0, stream>>>((const bf16*)x, perm, top, K, (bf16*)xs);
     return launch_status();
 }
 

@@ -80,7 +80,9 @@ def _declare(lib: ctypes.CDLL) -> None:
         "ems_rope_inplace": [P, I, I, I, I, I, I, I, I, P, P, P],
         "ems_latent_attention": [P, P, I, I, I, P, P, I, I, P, P, P, I, I, I, I, F, I, P, L, I, P],
         "ems_heads_gate": [P, P, I, P, I, I, I, I, P],
-        "ems_moe_route": [P, I, I, I, I, P, P, P, P, P, I, P],
+        "ems_moe_route": [P, I, I, I, I, P, P, P, P, P, I, I, P, I, P],
+        "ems_moe_gather": [P, P, I, I, I, P, P],
+        "ems_moe_up_grouped_tc05": [P, P, P, I, I, I, I, P, P],
         "ems_moe_up": [P, P, I, P, P, I, I, I, I, I, P, I, P],
         "ems_moe_down": [P, P, I, P, P, I, I, I, P, I, P],
         "ems_moe_combine": [P, P, P, I, I, I, I, P],
@@ -426,21 +428,55 @@ def moe_max_tiles(num_pairs: int, num_experts: int, tile_rows: int) -> int:
     return num_pairs // tile_rows + min(num_experts, num_pairs)
 
 
+MOE_BIG_TILE_ROWS = 256  # rows of a tile of the tcgen05 grouped product
+
+
 def moe_route(logits: torch.Tensor, top: int, renormalize: bool, ids: torch.Tensor, weights: torch.Tensor,
-              offsets: torch.Tensor, perm: torch.Tensor, plan: torch.Tensor, max_tiles: int) -> None:
+              offsets: torch.Tensor, perm: torch.Tensor, plan: torch.Tensor, max_tiles: int,
+              align: int = 1, big: torch.Tensor | None = None) -> None:
     """From router logits [N, E] (float32): softmax over all experts, the `top` largest per token
     (ids, weights: [N, top]; the weights are the scores, divided by their sum if `renormalize`),
     the first sorted row of every expert (offsets [E + 1], in a buffer of 3 E + 1: counters follow),
     the pairs t * top + k in expert order
     (perm [N * top]) and the tiles of the grouped products (plan: count, then expert / first row /
-    rows per tile)."""
+    rows per tile).  With `align` > 1 (steps of more than 512 tokens) every expert's sorted rows
+    start at a multiple of `align`, `perm` (len(big) * align entries) is -1 between them, and `big`
+    (int32) receives the expert of every group of `align` rows, -1 where none."""
     n, e = logits.shape
     assert logits.dtype == torch.float32 and weights.dtype == torch.float32
     assert ids.numel() >= n * top and weights.numel() >= n * top and perm.numel() >= n * top
     assert offsets.numel() >= 3 * e + 1 and plan.numel() >= 1 + 3 * max_tiles
+    max_big = 0 if big is None else big.numel()
+    assert align == 1 or (big is not None and perm.numel() >= max_big * align)
     _check(library().ems_moe_route(_ptr(logits, "logits"), n, e, top, 1 if renormalize else 0, _i32(ids, "ids"),
                                    _ptr(weights, "weights"), _i32(offsets, "offsets"), _i32(perm, "perm"),
-                                   _i32(plan, "plan"), max_tiles, _stream()), "moe_route")
+                                   _i32(plan, "plan"), max_tiles, align, _i32(big, "big"), max_big, _stream()),
+           "moe_route", 1 if n <= 512 else 4)
+
+
+def moe_gather(x: torch.Tensor, perm: torch.Tensor, top: int, xs: torch.Tensor) -> None:
+    """xs[i] = x[perm[i] // top] for the sorted rows i with perm[i] >= 0 (bfloat16, K a multiple of 8)."""
+    rows, k = xs.shape
+    assert x.shape[1] == k and x.dtype == xs.dtype == torch.bfloat16 and perm.numel() >= rows
+    _check(library().ems_moe_gather(_ptr(x, "x"), _i32(perm, "perm"), rows, top, k, _ptr(xs, "xs"), _stream()),
+           "moe_gather")
+
+
+def moe_up_grouped_tc05_supported(inter: int, k: int) -> bool:
+    """Whether the tcgen05 grouped gate/up product takes the sizes (SiLU only, bfloat16)."""
+    return inter % 128 == 0 and k % 8 == 0
+
+
+def moe_up_grouped_tc05(xs: torch.Tensor, wgu: torch.Tensor, big: torch.Tensor, out: torch.Tensor) -> None:
+    """out[i, :] = silu(xs[i] Wg[e]^T) * (xs[i] Wu[e]^T) for the rows of every group of 256 sorted rows
+    that `big` gives to an expert e (-1: the group is skipped): the two-SM tcgen05 kernel of prompt
+    steps in its grouped form.  xs: [len(big) * 256, K]; wgu: [E, 2 * ff, K]."""
+    e, ff2, k = wgu.shape
+    rows = xs.shape[0]
+    assert rows == big.numel() * MOE_BIG_TILE_ROWS and xs.shape[1] == k and out.shape == (rows, ff2 // 2)
+    assert xs.dtype == wgu.dtype == out.dtype == torch.bfloat16
+    _check(library().ems_moe_up_grouped_tc05(_ptr(xs, "xs"), _ptr(wgu, "wgu"), _ptr(out, "out"), rows, ff2 // 2, k,
+                                             e, _i32(big, "big"), _stream()), "moe_up_grouped_tc05")
 
 
 def moe_up(x: torch.Tensor, wgu: torch.Tensor, perm: torch.Tensor, offsets: torch.Tensor, plan: torch.Tensor,

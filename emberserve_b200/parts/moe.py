@@ -23,6 +23,11 @@ from emberserve_b200 import kernels as K
 from emberserve_b200.parts.base import FeedForward, ParamSpec, Source, StepContext, register_part
 
 
+# Steps of more tokens than this take the tcgen05 grouped product (the routing kernels lay the rows
+# out for it only in their several-block form, above 512 tokens).
+_GROUPED_TC05_TOKENS = 512
+
+
 @dataclass(frozen=True)
 class RoutedGLUSpec:
     hidden: int
@@ -72,8 +77,9 @@ class RoutedGLU(FeedForward):
 
     def scratch_elements_per_token(self) -> int:
         s: RoutedGLUSpec = self.spec
-        # activations of the chosen experts, their 32-bit outputs (two elements each), the result
-        return s.top_k * (s.intermediate + 2 * s.hidden) + 3 * s.hidden
+        # activations of the chosen experts, their 32-bit outputs (two elements each), the result; in
+        # prompt steps the gathered rows as well, and the padding of both to tiles of 256 rows
+        return 2 * s.top_k * (s.intermediate + 2 * s.hidden) + 3 * s.hidden
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         s: RoutedGLUSpec = self.spec
@@ -90,12 +96,28 @@ class RoutedGLU(FeedForward):
         ids = ctx.scratch("moe_ids", (pairs,), torch.int32)
         weights = ctx.scratch("moe_weights", (pairs,), torch.float32)
         offsets = ctx.scratch("moe_offsets", (3 * e + 1,), torch.int32)
-        perm = ctx.scratch("moe_perm", (pairs,), torch.int32)
         plan = ctx.scratch("moe_plan", (1 + 3 * max_tiles,), torch.int32)
-        K.moe_route(logits, top, s.renormalize, ids, weights, offsets, perm, plan, max_tiles)
-        act = ctx.scratch("moe_act", (pairs, s.intermediate), ctx.dtype)
-        K.moe_up(x, self.wgu.view(e, 2 * s.intermediate, s.hidden), perm, offsets, plan, max_tiles, top,
-                 s.activation, act)
+        wgu = self.wgu.view(e, 2 * s.intermediate, s.hidden)
+        # Prompt steps in bfloat16: every expert's sorted rows start at a multiple of 256, the rows are
+        # gathered into that layout, and the gate/up product runs on the two-SM tcgen05 kernel in its
+        # grouped form (the down product reads the same layout through the tile list).
+        if (x.is_cuda and ctx.dtype == torch.bfloat16 and n > _GROUPED_TC05_TOKENS and s.activation == "silu"
+                and K.moe_up_grouped_tc05_supported(s.intermediate, s.hidden)):
+            big_rows = K.MOE_BIG_TILE_ROWS
+            big = ctx.scratch("moe_big", (K.moe_max_tiles(pairs, e, big_rows),), torch.int32)
+            rows = big.numel() * big_rows
+            perm = ctx.scratch("moe_perm", (rows,), torch.int32)
+            K.moe_route(logits, top, s.renormalize, ids, weights, offsets, perm, plan, max_tiles, align=big_rows,
+                        big=big)
+            xs = ctx.scratch("moe_xs", (rows, s.hidden), ctx.dtype)
+            K.moe_gather(x, perm, top, xs)
+            act = ctx.scratch("moe_act", (rows, s.intermediate), ctx.dtype)
+            K.moe_up_grouped_tc05(xs, wgu, big, act)
+        else:
+            perm = ctx.scratch("moe_perm", (pairs,), torch.int32)
+            K.moe_route(logits, top, s.renormalize, ids, weights, offsets, perm, plan, max_tiles)
+            act = ctx.scratch("moe_act", (pairs, s.intermediate), ctx.dtype)
+            K.moe_up(x, wgu, perm, offsets, plan, max_tiles, top, s.activation, act)
         y = ctx.scratch("moe_y", (pairs, s.hidden), torch.float32)
         K.moe_down(act, self.wdown.view(e, s.hidden, s.intermediate), perm, offsets, plan, max_tiles, y)
         out = ctx.scratch("ffn_out", (n, s.hidden), ctx.dtype)

@@ -251,7 +251,8 @@ def test_latent_attention_finds_a_planted_key(dtype):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
 @pytest.mark.parametrize("n,experts,top,ff,width", [(1, 4, 1, 16, 64), (37, 5, 2, 24, 48), (300, 3, 3, 8, 40),
-                                                    (130, 10, 3, 88, 264), (20, 3, 2, 12, 36), (700, 6, 2, 200, 136)])
+                                                    (130, 10, 3, 88, 264), (20, 3, 2, 12, 36), (700, 6, 2, 200, 136),
+                                                    (900, 8, 2, 256, 192), (1500, 5, 3, 128, 64)])
 def test_routed_experts_against_plain(dtype, n, experts, top, ff, width):
     from emberserve_b200.parts.base import StepContext
     from emberserve_b200.parts.moe import RoutedGLU, RoutedGLUSpec
@@ -282,6 +283,7 @@ def test_routed_experts_against_plain(dtype, n, experts, top, ff, width):
     ctx = StepContext(num_tokens=n, num_rows=1, dtype=dtype, device=torch.device(DEV), tokens=None, positions=None,
                       row_of_token=None, cu_q=None, starts=None, q_lens=[n], start_list=[0], scratch=scratch)
     got = part.forward(x.to(DEV), ctx).cpu().double()
+    _K().check_status()  # (the last two shapes take the tcgen05 grouped product in bfloat16)
     want = plain.routed_experts(x.double(), {k: v.double() for k, v in w.items()}, experts, top)
     err = (got - want).abs().amax(-1) / want.abs().max()
     if dtype == torch.float32:
@@ -332,6 +334,42 @@ def test_routing_alone(n, experts, top):
         pl = plan.cpu().tolist()
         covered = sum(pl[3 + 3 * i] for i in range(pl[0]))
         assert covered == n * top and all(pl[3 + 3 * i] <= tile for i in range(pl[0]))
+
+
+def test_routing_laid_out_for_tiles_of_256_rows():
+    """The layout of prompt steps: every expert's rows start at a multiple of 256, the rows between
+    belong to nobody (-1), and every group of 256 rows names its expert or -1."""
+    K = _K()
+    n, experts, top, align = 1000, 7, 2, K.MOE_BIG_TILE_ROWS
+    g = torch.Generator().manual_seed(5)
+    logits = torch.randn(n, experts, generator=g) * 2
+    logits[:, 3] = -50.0  # an expert that nobody chooses
+    max_tiles = K.moe_max_tiles(n * top, experts, K.moe_tile_rows())
+    big = torch.empty(K.moe_max_tiles(n * top, experts, align), dtype=torch.int32, device=DEV)
+    ids = torch.empty(n * top, dtype=torch.int32, device=DEV)
+    wts = torch.empty(n * top, device=DEV)
+    offsets = torch.empty(3 * experts + 1, dtype=torch.int32, device=DEV)
+    perm = torch.empty(big.numel() * align, dtype=torch.int32, device=DEV)
+    plan = torch.empty(1 + 3 * max_tiles, dtype=torch.int32, device=DEV)
+    K.moe_route(logits.to(DEV), top, False, ids, wts, offsets, perm, plan, max_tiles, align=align, big=big)
+    off, p, flat, b = offsets.cpu().tolist(), perm.cpu().long(), ids.cpu().long(), big.cpu().tolist()
+    counts = torch.bincount(flat, minlength=experts).tolist()
+    assert counts[3] == 0
+    used = []
+    for e in range(experts):
+        assert off[e] % align == 0
+        rows = p[off[e]:off[e] + counts[e]]
+        assert bool((rows >= 0).all()) and bool((flat[rows] == e).all())
+        used += [e] * (-(-counts[e] // align))
+        end = off[e] + (-(-counts[e] // align)) * align
+        assert bool((p[off[e] + counts[e]:end] == -1).all())
+    assert b[:len(used)] == used and all(x == -1 for x in b[len(used):])
+    assert sorted(p[p >= 0].tolist()) == list(range(n * top))
+    pl = plan.cpu().tolist()
+    assert sum(pl[3 + 3 * i] for i in range(pl[0])) == n * top
+    for i in range(pl[0]):
+        e, row0, rows = pl[1 + 3 * i], pl[2 + 3 * i], pl[3 + 3 * i]
+        assert off[e] <= row0 and row0 + rows <= off[e] + counts[e]
 
 
 @pytest.mark.parametrize("act", ["relu", "silu", "gelu_tanh"])
