@@ -419,3 +419,27 @@ EMS_EXPORT int ems_moe_up_grouped_tc05(const void* xs, const void* w, void* act,
     p.expert_rows = 2 * inter;
     return launch_gemm_large<true>(mx, mw, p, stream);
 }
+
+// The down product of routed experts in the same layout: act [rows, k] (k = the experts' inner
+// width), w: [experts, n_out, k]; y[rows, n_out] (bfloat16) for the rows of tiles in use.  n_out and
+// k multiples of 8.
+EMS_EXPORT int ems_moe_down_grouped_tc05(const void* act, const void* w, void* y, int rows, int n_out, int k,
+                                         int experts, const int* tile_expert, cudaStream_t stream) {
+    if (rows <= 0 || n_out <= 0) return EMS_OK;
+    if (rows % (2 * GL_BM) || n_out % 8 || k <= 0 || k % 8 || experts <= 0) return EMS_ERR_SHAPE;
+    if (((uintptr_t)act % 16) || ((uintptr_t)w % 16) || ((uintptr_t)y % 16)) return EMS_ERR_ALIGN;
+    int* status = tc_status_device_ptr();
+    if (!status) return EMS_ERR_LAUNCH;
+    int* status_dev = nullptr;
+    if (cudaHostGetDevicePointer(reinterpret_cast<void**>(&status_dev), status, 0) != cudaSuccess) return EMS_ERR_LAUNCH;
+    CUtensorMap mx, mw;
+    if (!tc_tensor_map_2d(act, rows, k, GL_BM, &mx) || !tc_weight_map(w, (long long)n_out * experts, k, false, &mw))
+        return EMS_ERR_LAUNCH;
+    GemmLargeParams p;
+    p.y = reinterpret_cast<bf16*>(y); p.bias = nullptr; p.status = status_dev; p.m_tok = rows; p.n_out = n_out;
+    p.k_tiles = (k + GL_BK - 1) / GL_BK; p.m_tiles = rows / (2 * GL_BM); p.n_tiles = (n_out + 2 * GL_BN - 1) / (2 * GL_BN);
+    p.tiled = 0;
+    p.tile_expert = tile_expert;
+    p.expert_rows = n_out;
+    return launch_gemm_large<false>(mx, mw, p, stream);
+}

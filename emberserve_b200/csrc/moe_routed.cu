@@ -195,12 +195,15 @@ __global__ void moe_gather_kernel(const bf16* __restrict__ x, const int* __restr
     for (int c = threadIdx.x; c < K / 8; c += blockDim.x) dst[c] = src[c];
 }
 
+// inv (optional): the sorted row of every pair, the inverse of perm
 __global__ void moe_scatter_kernel(const int* __restrict__ ids, int pairs, const int* __restrict__ offsets,
-                                   int* __restrict__ cursor, int* __restrict__ perm) {
+                                   int* __restrict__ cursor, int* __restrict__ perm, int* __restrict__ inv) {
     const int p = blockIdx.x * blockDim.x + threadIdx.x;
     if (p >= pairs) return;
     const int e = ids[p];
-    perm[offsets[e] + atomicAdd(&cursor[e], 1)] = p;
+    const int row = offsets[e] + atomicAdd(&cursor[e], 1);
+    perm[row] = p;
+    if (inv) inv[p] = row;
 }
 
 __device__ __forceinline__ float moe_activation(float g, int act) {
@@ -452,18 +455,40 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const float* __r
     }
 }
 
+// out[t, :] = sum_k wts[t, k] * y[inv[t * top + k], :] for y in bfloat16 in the sorted layout
+__global__ void moe_combine_rows_kernel(const bf16* __restrict__ y, const int* __restrict__ inv,
+                                        const float* __restrict__ wts, bf16* __restrict__ out, int top, int H) {
+    const size_t t = blockIdx.x;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float s = 0.f;
+        for (int k = 0; k < top; ++k)
+            s = fmaf(wts[t * top + k], __bfloat162float(y[(size_t)inv[t * top + k] * H + c]), s);
+        out[t * H + c] = __float2bfloat16_rn(s);
+    }
+}
+
 }  // namespace ems
 
 using namespace ems;
+
+EMS_EXPORT int ems_moe_combine_rows(const void* y, const int* inv, const float* wts, void* out, int n, int top, int H,
+                                    cudaStream_t stream) {
+    if (n <= 0) return EMS_OK;
+    int th = 32;
+    while (th < H && th < 256) th <<= 1;
+    moe_combine_rows_kernel<<<n, th, 0, stream>>>((const bf16*)y, inv, wts, (bf16*)out, top, H);
+    return launch_status();
+}
 
 EMS_EXPORT int ems_moe_tile_rows() { return MOE_TM; }
 
 // align > 1 (steps of more than 512 tokens only): every expert's sorted rows start at a multiple of
 // `align`; perm (max_big * align entries) holds -1 for the rows between, and big[0 .. max_big) names
-// the expert of every group of `align` rows (-1: not in use).
+// the expert of every group of `align` rows (-1: not in use); inv (optional, same steps) receives the
+// sorted row of every pair.
 EMS_EXPORT int ems_moe_route(const float* logits, int n, int E, int top, int renorm, int* ids, float* wts,
                              int* offsets, int* perm, int* plan, int max_tiles, int align, int* big, int max_big,
-                             cudaStream_t stream) {
+                             int* inv, cudaStream_t stream) {
     if (n <= 0) return EMS_OK;
     if (top < 1 || top > E) return EMS_ERR_SHAPE;
     if (align < 1 || (align > 1 && (n <= 512 || !big || max_big < n * top / align + (E < n * top ? E : n * top))))
@@ -480,7 +505,7 @@ EMS_EXPORT int ems_moe_route(const float* logits, int n, int E, int top, int ren
             return EMS_ERR_LAUNCH;
         moe_plan_kernel<<<1, 32, 0, stream>>>(E, counts, cursor, offsets, plan, max_tiles, align,
                                               align > 1 ? big : nullptr, max_big);
-        moe_scatter_kernel<<<(n * top + 255) / 256, 256, 0, stream>>>(ids, n * top, offsets, cursor, perm);
+        moe_scatter_kernel<<<(n * top + 255) / 256, 256, 0, stream>>>(ids, n * top, offsets, cursor, perm, inv);
         return launch_status();
     }
     int th = 32 * (n < 32 ? n : 32);  // a warp per token, up to 32 warps

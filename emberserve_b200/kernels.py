@@ -80,7 +80,9 @@ def _declare(lib: ctypes.CDLL) -> None:
         "ems_rope_inplace": [P, I, I, I, I, I, I, I, I, P, P, P],
         "ems_latent_attention": [P, P, I, I, I, P, P, I, I, P, P, P, I, I, I, I, F, I, P, L, I, P],
         "ems_heads_gate": [P, P, I, P, I, I, I, I, P],
-        "ems_moe_route": [P, I, I, I, I, P, P, P, P, P, I, I, P, I, P],
+        "ems_moe_route": [P, I, I, I, I, P, P, P, P, P, I, I, P, I, P, P],
+        "ems_moe_down_grouped_tc05": [P, P, P, I, I, I, I, P, P],
+        "ems_moe_combine_rows": [P, P, P, P, I, I, I, P],
         "ems_moe_gather": [P, P, I, I, I, P, P],
         "ems_moe_up_grouped_tc05": [P, P, P, I, I, I, I, P, P],
         "ems_moe_up": [P, P, I, P, P, I, I, I, I, I, P, I, P],
@@ -433,7 +435,7 @@ MOE_BIG_TILE_ROWS = 256  # rows of a tile of the tcgen05 grouped product
 
 def moe_route(logits: torch.Tensor, top: int, renormalize: bool, ids: torch.Tensor, weights: torch.Tensor,
               offsets: torch.Tensor, perm: torch.Tensor, plan: torch.Tensor, max_tiles: int,
-              align: int = 1, big: torch.Tensor | None = None) -> None:
+              align: int = 1, big: torch.Tensor | None = None, inv: torch.Tensor | None = None) -> None:
     """From router logits [N, E] (float32): softmax over all experts, the `top` largest per token
     (ids, weights: [N, top]; the weights are the scores, divided by their sum if `renormalize`),
     the first sorted row of every expert (offsets [E + 1], in a buffer of 3 E + 1: counters follow),
@@ -441,7 +443,8 @@ def moe_route(logits: torch.Tensor, top: int, renormalize: bool, ids: torch.Tens
     (perm [N * top]) and the tiles of the grouped products (plan: count, then expert / first row /
     rows per tile).  With `align` > 1 (steps of more than 512 tokens) every expert's sorted rows
     start at a multiple of `align`, `perm` (len(big) * align entries) is -1 between them, and `big`
-    (int32) receives the expert of every group of `align` rows, -1 where none."""
+    (int32) receives the expert of every group of `align` rows, -1 where none; `inv` (optional, the
+    same steps) receives the sorted row of every pair."""
     n, e = logits.shape
     assert logits.dtype == torch.float32 and weights.dtype == torch.float32
     assert ids.numel() >= n * top and weights.numel() >= n * top and perm.numel() >= n * top
@@ -450,7 +453,8 @@ def moe_route(logits: torch.Tensor, top: int, renormalize: bool, ids: torch.Tens
     assert align == 1 or (big is not None and perm.numel() >= max_big * align)
     _check(library().ems_moe_route(_ptr(logits, "logits"), n, e, top, 1 if renormalize else 0, _i32(ids, "ids"),
                                    _ptr(weights, "weights"), _i32(offsets, "offsets"), _i32(perm, "perm"),
-                                   _i32(plan, "plan"), max_tiles, align, _i32(big, "big"), max_big, _stream()),
+                                   _i32(plan, "plan"), max_tiles, align, _i32(big, "big"), max_big,
+                                   _i32(inv, "inv"), _stream()),
            "moe_route", 1 if n <= 512 else 4)
 
 
@@ -500,6 +504,26 @@ def moe_down(act: torch.Tensor, wdown: torch.Tensor, perm: torch.Tensor, offsets
     _check(library().ems_moe_down(_ptr(act, "act"), _ptr(wdown, "wdown"), _dt(act), _i32(perm, "perm"),
                                   _i32(plan, "plan"), max_tiles, h, ff, _ptr(y, "y"),
                                   1 if kernel == "generic" else 0, _stream()), "moe_down")
+
+
+def moe_down_grouped_tc05(act: torch.Tensor, wdown: torch.Tensor, big: torch.Tensor, y: torch.Tensor) -> None:
+    """y[i, :] = act[i, :] Wd[e]^T (bfloat16) for the rows of every group of 256 sorted rows that `big`
+    gives to an expert e: the grouped tcgen05 kernel.  wdown: [E, H, ff]."""
+    e, h, ff = wdown.shape
+    rows = act.shape[0]
+    assert rows == big.numel() * MOE_BIG_TILE_ROWS and act.shape[1] == ff and y.shape == (rows, h)
+    assert act.dtype == wdown.dtype == y.dtype == torch.bfloat16
+    _check(library().ems_moe_down_grouped_tc05(_ptr(act, "act"), _ptr(wdown, "wdown"), _ptr(y, "y"), rows, h, ff, e,
+                                               _i32(big, "big"), _stream()), "moe_down_grouped_tc05")
+
+
+def moe_combine_rows(y: torch.Tensor, inv: torch.Tensor, weights: torch.Tensor, out: torch.Tensor, top: int) -> None:
+    """out[t, :] = sum_k weights[t, k] * y[inv[t * top + k], :] (k ascending) for bfloat16 rows `y` in the
+    sorted layout."""
+    n, h = out.shape
+    assert y.dtype == out.dtype == torch.bfloat16 and weights.dtype == torch.float32 and y.shape[1] == h
+    _check(library().ems_moe_combine_rows(_ptr(y, "y"), _i32(inv, "inv"), _ptr(weights, "weights"), _ptr(out, "out"),
+                                          n, top, h, _stream()), "moe_combine_rows")
 
 
 def moe_combine(y: torch.Tensor, weights: torch.Tensor, out: torch.Tensor, top: int) -> None:

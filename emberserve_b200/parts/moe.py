@@ -107,12 +107,19 @@ class RoutedGLU(FeedForward):
             big = ctx.scratch("moe_big", (K.moe_max_tiles(pairs, e, big_rows),), torch.int32)
             rows = big.numel() * big_rows
             perm = ctx.scratch("moe_perm", (rows,), torch.int32)
+            inv = ctx.scratch("moe_inv", (pairs,), torch.int32)
             K.moe_route(logits, top, s.renormalize, ids, weights, offsets, perm, plan, max_tiles, align=big_rows,
-                        big=big)
+                        big=big, inv=inv)
             xs = ctx.scratch("moe_xs", (rows, s.hidden), ctx.dtype)
             K.moe_gather(x, perm, top, xs)
             act = ctx.scratch("moe_act", (rows, s.intermediate), ctx.dtype)
             K.moe_up_grouped_tc05(xs, wgu, big, act)
+            if s.intermediate % 8 == 0 and s.hidden % 8 == 0:  # the down product in the same form
+                y16 = ctx.scratch("moe_y16", (rows, s.hidden), ctx.dtype)
+                K.moe_down_grouped_tc05(act, self.wdown.view(e, s.hidden, s.intermediate), big, y16)
+                out = ctx.scratch("ffn_out", (n, s.hidden), ctx.dtype)
+                K.moe_combine_rows(y16, inv, weights, out, top)
+                return out
         else:
             perm = ctx.scratch("moe_perm", (pairs,), torch.int32)
             K.moe_route(logits, top, s.renormalize, ids, weights, offsets, perm, plan, max_tiles)

@@ -360,7 +360,7 @@ def moe_max_tiles(num_pairs, num_experts, tile_rows):
     return num_pairs // tile_rows + min(num_experts, num_pairs)
 
 
-def moe_route(logits, top, renormalize, ids, weights, offsets, perm, plan, max_tiles, align=1, big=None):
+def moe_route(logits, top, renormalize, ids, weights, offsets, perm, plan, max_tiles, align=1, big=None, inv=None):
     assert align == 1, "the aligned layout belongs to the GPU path"
     n, e = logits.shape
     s = torch.softmax(logits.float(), -1)

@@ -553,3 +553,25 @@ def test_command_line_random_weights_then_generate(tmp_path):
         capture_output=True, text=True, cwd=ROOT, timeout=600)
     assert proc.returncode == 0, proc.stderr[-1500:]
     assert [int(t) for t in proc.stdout.split()] == want.output_token_ids
+
+
+def test_long_prompt_steps_take_the_grouped_tensor_core_products(tmp_path):
+    """A prompt of 700 tokens in one step (more than 512 tokens: the experts' products run in their
+    tcgen05 grouped form, rows laid out in tiles of 256) gives the logits of the same prompt in
+    portions of 200 (the mma.sync kernels), and both follow the 64-bit oracle as closely as bfloat16
+    allows.  Experts of 128 x 64 are the smallest the grouped form takes."""
+    cfg = json.loads(json.dumps(td.DAM_B))
+    cfg["max_positions"] = 1024
+    cfg["layers"][0]["mlp"] = {"kind": "moe", "expert": {"ff": 128}, "router": {"experts": 6, "top": 2}}
+    cfg["layers"][1]["mlp"] = {"kind": "moe", "expert": {"ff": 256}, "router": {"experts": 3, "top": 3}}
+    model = td.write_model(cfg, tmp_path / "m", seed=31)
+    reqs = rc.make_requests(cfg["vocab"], [700], seed=2)
+    want = _oracle(model, reqs)
+    scale = float(np.abs(want["r0"]).max())
+    whole = _replay(model, "dam_b", torch.bfloat16, rc.whole(reqs))
+    parts = _replay(model, "dam_b", torch.bfloat16, rc.portions(reqs, sizes=(200, 150, 190)))
+    _K().check_status()
+    _compare(whole, want, reqs, scale, torch.bfloat16, "one step")
+    _compare(parts, want, reqs, scale, torch.bfloat16, "portions")
+    errs = np.array([float(np.abs(whole[k] - parts[k]).max()) for k in whole]) / scale
+    assert np.median(errs) <= TOL16 / 4 and np.mean(errs > TOL16) <= 0.10
