@@ -159,6 +159,14 @@ gemm_large_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
     const uint32_t rank = cluster_rank();          // 0 leads: it issues the MMAs and owns full / tempty
     const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
     const int total = p.m_tiles * p.n_tiles;
+    // Which tile comes when.  One weight for all rows: the tiles in flight share few weight rows (they
+    // are read from memory once and from L2 after that).  Grouped: every row tile has weights of its
+    // own, read once whatever the order, so the tiles in flight share few ROW tiles instead (walking
+    // the experts' rows once per column tile re-read them from memory: 1.66 GB per call against 0.8).
+    auto split = [&](int tile, int& m_tile, int& n_tile) {
+        if (p.tile_expert) { m_tile = tile / p.n_tiles; n_tile = tile % p.n_tiles; }
+        else { n_tile = tile / p.m_tiles; m_tile = tile % p.m_tiles; }
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < GL_STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
@@ -200,7 +208,8 @@ gemm_large_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
         }
         grid_dependency_wait();
         for (int tile = pair; tile < total && ok; tile += pairs) {
-            const int n_tile = tile / p.m_tiles, m_tile = tile % p.m_tiles;
+            int n_tile, m_tile;
+            split(tile, m_tile, n_tile);
             const int expert = p.tile_expert ? p.tile_expert[m_tile] : 0;
             if (expert < 0) continue;
             const int x_row = m_tile * 2 * GL_BM + (int)rank * GL_BM;
@@ -231,7 +240,7 @@ gemm_large_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
         bool ok = true;
         int it = 0, si = 0;
         for (int tile = pair; tile < total && ok; tile += pairs) {
-            if (p.tile_expert && p.tile_expert[tile % p.m_tiles] < 0) continue;
+            if (p.tile_expert && p.tile_expert[tile / p.n_tiles] < 0) continue;
             const int b = si & 1;
             const uint32_t tph = (uint32_t)(si >> 1) & 1u;
             // both blocks have drained this accumulator
@@ -279,7 +288,8 @@ gemm_large_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
         int si = 0;
         if (p.tile_expert) grid_dependency_wait();
         for (int tile = pair; tile < total && ok; tile += pairs) {
-            const int n_tile = tile / p.m_tiles, m_tile = tile % p.m_tiles;
+            int n_tile, m_tile;
+            split(tile, m_tile, n_tile);
             if (p.tile_expert && p.tile_expert[m_tile] < 0) continue;
             const int b = si & 1;
             const uint32_t tph = (uint32_t)(si >> 1) & 1u;
