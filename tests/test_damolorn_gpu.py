@@ -564,12 +564,14 @@ def test_long_prompt_steps_take_the_grouped_tensor_core_products(tmp_path):
     cfg["max_positions"] = 1024
     cfg["layers"][0]["mlp"] = {"kind": "moe", "expert": {"ff": 128}, "router": {"experts": 6, "top": 2}}
     cfg["layers"][1]["mlp"] = {"kind": "moe", "expert": {"ff": 256}, "router": {"experts": 3, "top": 3}}
+    # (a latent of 256 numbers: the attention kernel with eight warps)
+    cfg["layers"][1]["mixer"] = td._mixer(5, 4, 16, 16, 8, 256, 28, 200000.0)
     model = td.write_model(cfg, tmp_path / "m", seed=31)
     reqs = rc.make_requests(cfg["vocab"], [700], seed=2)
     want = _oracle(model, reqs)
     scale = float(np.abs(want["r0"]).max())
     whole = _replay(model, "dam_b", torch.bfloat16, rc.whole(reqs))
-    parts = _replay(model, "dam_b", torch.bfloat16, rc.portions(reqs, sizes=(200, 150, 190)))
+    parts = _replay(model, "dam_b", torch.bfloat16, rc.portions(reqs, sizes=(200, 1, 150, 3, 190)))
     _K().check_status()
     _compare(whole, want, reqs, scale, torch.bfloat16, "one step")
     _compare(parts, want, reqs, scale, torch.bfloat16, "portions")
