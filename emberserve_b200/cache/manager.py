@@ -4,7 +4,8 @@ per *group* of cache entries, and slots of fixed-size state.  Pure Python, no te
 Cache entries (one per layer call that keeps something) with equal needs form a group.
 Every paged group has pages of its own: its own pool, its own block table per request.
 A group whose entries read only a window of keys gives pages back as soon as the window
-has passed them; a request that ends gives back everything.  Freed pages go to the back
+has passed them (likewise a group whose entries read only the chunk of positions they stand in);
+a request that ends gives back everything.  Freed pages go to the back
 of the pool and are handed out again from the front, with whatever they still contain
 (``emberserve/kv/block_manager.py:69-72,132-152``: same deque discipline, same
 ``allocate`` / ``append_slots`` / ``free`` life cycle, reference counts kept for sharing).
@@ -141,6 +142,7 @@ class CacheManager:
             raise ValueError("one page count per paged group is needed")
         self.pools = [PagePool(n) for n in counts]
         self.windows: list[int | None] = [self.groups[i].need.window for i in self.paged_groups]
+        self.chunks: list[int | None] = [getattr(self.groups[i].need, "chunk", None) for i in self.paged_groups]
         self.num_state_slots = num_state_slots if self.state_groups else 0
         self._free_slots: deque[int] = deque(range(self.num_state_slots))
         self._fresh_slots: set[int] = set()
@@ -246,11 +248,14 @@ class CacheManager:
         self._release_passed(seq)
 
     def _release_passed(self, seq: _Sequence) -> None:
-        for k, window in enumerate(self.windows):
-            if window is None:
+        for k, (window, chunk) in enumerate(zip(self.windows, self.chunks)):
+            if window is None and chunk is None:
                 continue
-            # The next query stands at position >= committed and reads keys > committed - window.
-            first_needed = max(0, seq.committed - window + 1)
+            # The next query stands at position >= committed and reads keys > committed - window,
+            # and none before the chunk that position `committed` lies in.
+            first_needed = 0 if window is None else max(0, seq.committed - window + 1)
+            if chunk is not None:
+                first_needed = max(first_needed, (seq.committed // chunk) * chunk)
             upto = min(first_needed // self.page_size, len(seq.tables[k]))
             table = seq.tables[k]
             for i in range(seq.released[k], upto):

@@ -85,7 +85,7 @@ class CacheStorage:
         t = self.tensors[gi]
         if isinstance(need, PagedKV):
             return PagedKVHandle(k=t[j, 0], v=t[j, 1], block_tables=block_tables[pk],
-                                 page_size=self.page_size, window=need.window, write=write)
+                                 page_size=self.page_size, window=need.window, write=write, chunk=need.chunk)
         if isinstance(need, PagedLatent):
             return PagedLatentHandle(pages=t[j], block_tables=block_tables[pk], page_size=self.page_size,
                                      window=need.window, write=write)

@@ -1,6 +1,7 @@
 from emberserve_b200.config.engine import EngineConfig, dtype_from_str
 from emberserve_b200.config.damolorn import DamolornConfig
+from emberserve_b200.config.dedizen import DedizenConfig
 from emberserve_b200.config.model import ConfigError, ModelConfig, Qwen2Config, read_config_json
 
-__all__ = ["ConfigError", "DamolornConfig", "EngineConfig", "ModelConfig", "Qwen2Config", "dtype_from_str",
+__all__ = ["ConfigError", "DamolornConfig", "DedizenConfig", "EngineConfig", "ModelConfig", "Qwen2Config", "dtype_from_str",
            "read_config_json"]

@@ -37,7 +37,19 @@ struct AttnParams {
     long long q_stride;
     int bt_stride, page_size, nh, nkv, D, G, window, splits;
     float scale;
+    // Beyond the plain causal form (all optional):
+    int chunk = 0;                  // > 0: the query at p sees only keys j with j / chunk == p / chunk
+    const float* sinks = nullptr;   // [nh] float: exp(sinks[h]) joins the softmax's denominator (no key, no value)
+    const void* gate = nullptr;     // [N, gate_stride]: head h's output is multiplied by sigmoid(gate[n, h])
+    long long gate_stride = 0;
 };
+
+// The first key that the query at position p may see.
+__device__ __forceinline__ int first_visible(int p, int window, int chunk) {
+    int lo = window > 0 ? max(0, p - window + 1) : 0;
+    if (chunk > 0) lo = max(lo, (p / chunk) * chunk);
+    return lo;
+}
 
 template <typename T, int VEC> struct VecLoad;
 template <> struct VecLoad<float, 4> {
@@ -82,7 +94,7 @@ paged_attention_kernel(const AttnParams p) {
     const int tok_lo = r0 / G;
     const int tok_hi = min(nrows - 1, r0 + BQ - 1) / G;
     const int p_lo = start + tok_lo, p_hi = start + tok_hi;
-    const int k_begin = p.window > 0 ? max(0, p_lo - p.window + 1) : 0;
+    const int k_begin = first_visible(p_lo, p.window, p.chunk);
     const int k_end = p_hi + 1;
     const int kt0 = (k_begin / BK) * BK;
     const int ntiles = (k_end - kt0 + BK - 1) / BK;
@@ -111,13 +123,14 @@ paged_attention_kernel(const AttnParams p) {
     }
 
     float m[RPW], l[RPW], o[RPW][DCH];
-    int qpos[RPW];
+    int qpos[RPW], qlo[RPW];
 #pragma unroll
     for (int r = 0; r < RPW; ++r) {
         m[r] = -INFINITY;
         l[r] = 0.f;
         const int gr = r0 + warp * RPW + r;
         qpos[r] = gr < nrows ? start + gr / G : -1;   // -1: no key is visible
+        qlo[r] = gr < nrows ? first_visible(qpos[r], p.window, p.chunk) : 0;
 #pragma unroll
         for (int c = 0; c < DCH; ++c) o[r][c] = 0.f;
     }
@@ -161,7 +174,7 @@ paged_attention_kernel(const AttnParams p) {
         const int key = kt + lane;
 #pragma unroll
         for (int r = 0; r < RPW; ++r) {
-            const bool visible = key <= qpos[r] && (p.window <= 0 || key > qpos[r] - p.window);
+            const bool visible = key <= qpos[r] && key >= qlo[r];
             const float s = visible ? acc[r] * p.scale : -INFINITY;
             const float m_new = fmaxf(m[r], warp_max(s));
             const float pe = visible ? expf(s - m_new) : 0.f;
@@ -200,7 +213,9 @@ paged_attention_kernel(const AttnParams p) {
         const size_t prow = (size_t)(q0 + tok) * p.nh + head;
         if (p.splits == 1) {
             T* dst = reinterpret_cast<T*>(p.out) + prow * D;
-            const float inv = 1.0f / l[r];
+            float inv = 1.0f / (p.sinks ? l[r] + expf(p.sinks[head] - m[r]) : l[r]);
+            if (p.gate)
+                inv *= 1.f / (1.f + expf(-to_f32<T>(reinterpret_cast<const T*>(p.gate)[(size_t)(q0 + tok) * p.gate_stride + head])));
 #pragma unroll
             for (int c = 0; c < DCH; ++c) {
                 const int d = lane + 32 * c;
@@ -229,7 +244,8 @@ constexpr int MERGE_MAX_SPLITS = 256;
 template <typename T>
 __global__ void attention_merge_kernel(const float* __restrict__ part_o,
                                        const float* __restrict__ part_ml, T* __restrict__ out,
-                                       int splits, int D) {
+                                       int splits, int D, const float* __restrict__ sinks, int nh,
+                                       const T* __restrict__ gate, long long gate_stride) {
     pdl_prologue();
     __shared__ float weight[MERGE_MAX_SPLITS];
     __shared__ float red[33];
@@ -247,7 +263,10 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o,
         weight[s] = f;
         d_loc += ml[s * 2 + 1] * f;
     }
-    const float inv = 1.0f / block_sum(d_loc, red);  // (block_sum synchronises: the weights are written)
+    float inv = block_sum(d_loc, red);  // (block_sum synchronises: the weights are written)
+    if (sinks) inv += expf(sinks[prow % nh] - M);
+    inv = 1.0f / inv;
+    if (gate) inv *= 1.f / (1.f + expf(-to_f32<T>(gate[(prow / nh) * gate_stride + prow % nh])));
     const float* po = part_o + prow * splits * D;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float acc = 0.f;
@@ -299,7 +318,8 @@ int run_attention(const AttnParams& p, int B, int N, int max_q_len, cudaStream_t
     if (rc != EMS_OK || p.splits == 1) return rc;
     const int threads = p.D >= 128 ? 128 : 64;
     attention_merge_kernel<T><<<(unsigned)((size_t)N * p.nh), threads, 0, stream>>>(
-        p.part_o, p.part_ml, reinterpret_cast<T*>(p.out), p.splits, p.D);
+        p.part_o, p.part_ml, reinterpret_cast<T*>(p.out), p.splits, p.D, p.sinks, p.nh,
+        reinterpret_cast<const T*>(p.gate), p.gate_stride);
     return launch_status();
 }
 
@@ -313,19 +333,25 @@ EMS_EXPORT long long ems_paged_attention_scratch_bytes(int N, int nh, int D, int
     return (long long)N * nh * splits * (D + 2) * (long long)sizeof(float);
 }
 
-EMS_EXPORT int ems_paged_attention(const void* q, long long q_stride, void* out, int dtype,
-                                   const void* kcache, const void* vcache, const int* block_tables,
-                                   int bt_stride, int page_size, const int* cu_q, const int* starts,
-                                   int B, int N, int nh, int nkv, int D, int window, float scale,
-                                   int max_q_len, int splits, void* scratch, long long scratch_bytes,
-                                   int impl, cudaStream_t stream) {
+static int paged_attention_any(const void* q, long long q_stride, void* out, int dtype,
+                               const void* kcache, const void* vcache, const int* block_tables,
+                               int bt_stride, int page_size, const int* cu_q, const int* starts,
+                               int B, int N, int nh, int nkv, int D, int window, float scale,
+                               int max_q_len, int splits, void* scratch, long long scratch_bytes,
+                               int impl, int chunk, const float* sinks, const void* gate, long long gate_stride,
+                               cudaStream_t stream) {
     // impl: 0 = the fastest kernel that takes the case, 1 = the generic kernel, 2 = the
     // tcgen05 prompt kernel or an error, 3 = the mma.sync kernels where they take the case.
     if (B <= 0 || N <= 0) return EMS_OK;
-    if (D <= 0 || D % 16 || D > 256 || nkv <= 0 || nh % nkv || page_size <= 0 || splits < 1 ||
-        splits > MERGE_MAX_SPLITS)
-        return EMS_ERR_SHAPE;
     const int esize = dtype == EMS_F32 ? 4 : 2;
+    // (rows of a head are moved 16 bytes at a time)
+    if (D <= 0 || D % (16 / esize) || D > 256 || nkv <= 0 || nh % nkv || page_size <= 0 || splits < 1 ||
+        splits > MERGE_MAX_SPLITS || chunk < 0)
+        return EMS_ERR_SHAPE;
+    // the tensor-core kernels know the plain causal form (and a window)
+    const bool plain = chunk <= 0 && !sinks && !gate;
+    if (!plain && impl == 2) return EMS_ERR_SHAPE;
+    if (!plain) impl = 1;
     if ((q_stride * esize) % 16 || ((uintptr_t)q % 16) || ((uintptr_t)kcache % 16) || ((uintptr_t)vcache % 16))
         return EMS_ERR_ALIGN;
     AttnParams p;
@@ -333,6 +359,7 @@ EMS_EXPORT int ems_paged_attention(const void* q, long long q_stride, void* out,
     p.starts = starts; p.q_stride = q_stride; p.bt_stride = bt_stride; p.page_size = page_size;
     p.nh = nh; p.nkv = nkv; p.D = D; p.G = nh / nkv; p.window = window; p.splits = splits;
     p.scale = scale; p.part_o = nullptr; p.part_ml = nullptr;
+    p.chunk = chunk; p.sinks = sinks; p.gate = gate; p.gate_stride = gate_stride;
     if (splits > 1) {
         if (scratch == nullptr || scratch_bytes < ems_paged_attention_scratch_bytes(N, nh, D, splits))
             return EMS_ERR_SCRATCH;
@@ -362,11 +389,36 @@ EMS_EXPORT int ems_paged_attention(const void* q, long long q_stride, void* out,
         if (rc != EMS_OK || splits == 1) return rc;
         return launch_pdl(attention_merge_kernel<bf16>, dim3((unsigned)((size_t)N * nh)), dim3(D >= 128 ? 128 : 64),
                           0, stream, (const float*)p.part_o, (const float*)p.part_ml, reinterpret_cast<bf16*>(out),
-                          splits, D);
+                          splits, D, (const float*)nullptr, nh, (const bf16*)nullptr, 0LL);
     }
     if (dtype == EMS_F32) return run_attention<float>(p, B, N, max_q_len, stream);
     if (dtype == EMS_BF16) return run_attention<bf16>(p, B, N, max_q_len, stream);
     return EMS_ERR_DTYPE;
+}
+
+EMS_EXPORT int ems_paged_attention(const void* q, long long q_stride, void* out, int dtype,
+                                   const void* kcache, const void* vcache, const int* block_tables,
+                                   int bt_stride, int page_size, const int* cu_q, const int* starts,
+                                   int B, int N, int nh, int nkv, int D, int window, float scale,
+                                   int max_q_len, int splits, void* scratch, long long scratch_bytes,
+                                   int impl, cudaStream_t stream) {
+    return paged_attention_any(q, q_stride, out, dtype, kcache, vcache, block_tables, bt_stride, page_size, cu_q,
+                               starts, B, N, nh, nkv, D, window, scale, max_q_len, splits, scratch, scratch_bytes,
+                               impl, 0, nullptr, nullptr, 0, stream);
+}
+
+// The same with a chunk mask, a sink per head in the softmax's denominator and a sigmoid gate per
+// (token, head) on the output; each is optional (0 / null).
+EMS_EXPORT int ems_paged_attention_masked(const void* q, long long q_stride, void* out, int dtype,
+                                          const void* kcache, const void* vcache, const int* block_tables,
+                                          int bt_stride, int page_size, const int* cu_q, const int* starts,
+                                          int B, int N, int nh, int nkv, int D, int window, int chunk,
+                                          const float* sinks, const void* gate, long long gate_stride, float scale,
+                                          int max_q_len, int splits, void* scratch, long long scratch_bytes,
+                                          int impl, cudaStream_t stream) {
+    return paged_attention_any(q, q_stride, out, dtype, kcache, vcache, block_tables, bt_stride, page_size, cu_q,
+                               starts, B, N, nh, nkv, D, window, scale, max_q_len, splits, scratch, scratch_bytes,
+                               impl, chunk, sinks, gate, gate_stride, stream);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -455,5 +507,6 @@ EMS_EXPORT int ems_decode_attention_fused(const void* qkv, long long q_stride, v
     const int rc = run_decode_mma(d, B, D, stream);
     if (rc != EMS_OK || splits == 1) return rc;
     return launch_pdl(attention_merge_kernel<bf16>, dim3((unsigned)((size_t)B * nh)), dim3(D >= 128 ? 128 : 64), 0,
-                      stream, (const float*)d.part_o, (const float*)d.part_ml, reinterpret_cast<bf16*>(out), splits, D);
+                      stream, (const float*)d.part_o, (const float*)d.part_ml, reinterpret_cast<bf16*>(out), splits, D,
+                      (const float*)nullptr, nh, (const bf16*)nullptr, 0LL);
 }

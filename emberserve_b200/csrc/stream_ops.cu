@@ -251,7 +251,8 @@ __global__ void glu_act_kernel(const T* __restrict__ gu, T* __restrict__ out, in
 // taps - 1 inputs of each request in time order (zero where the request has not begun).
 
 template <typename T>
-__global__ void causal_taps_kernel(const T* __restrict__ x, const void* __restrict__ w, int w_dtype,
+__global__ void causal_taps_kernel(const T* __restrict__ x, long long ldx, const void* __restrict__ w, int w_dtype,
+                                   const void* __restrict__ bias, int identity,
                                    const float* __restrict__ state, const int* __restrict__ slots,
                                    const int* __restrict__ cu_q, const int* __restrict__ row_of_token,
                                    T* __restrict__ out, int C, int taps) {
@@ -261,15 +262,15 @@ __global__ void causal_taps_kernel(const T* __restrict__ x, const void* __restri
     const int local = t - first;
     const float* st = state ? state + (size_t)slots[row] * (taps - 1) * C : nullptr;
     for (int c = threadIdx.x; c < C; c += blockDim.x) {
-        float conv = 0.f;
+        float conv = bias ? load_any(bias, w_dtype, c) : 0.f;
         for (int j = 0; j < taps; ++j) {
             const int s = local - (taps - 1) + j;
             float v;
-            if (s >= 0) v = to_f32<T>(x[(size_t)(first + s) * C + c]);
+            if (s >= 0) v = to_f32<T>(x[(size_t)(first + s) * ldx + c]);
             else v = st ? st[(size_t)(taps - 1 + s) * C + c] : 0.f;
             conv += load_any(w, w_dtype, (size_t)c * taps + j) * v;
         }
-        out[(size_t)t * C + c] = from_f32<T>(to_f32<T>(x[(size_t)t * C + c]) + conv);
+        out[(size_t)t * C + c] = from_f32<T>(identity ? to_f32<T>(x[(size_t)t * ldx + c]) + conv : conv);
     }
 }
 
@@ -277,7 +278,7 @@ __global__ void causal_taps_kernel(const T* __restrict__ x, const void* __restri
 // step's tokens and, where the row brought fewer, from the old state moved up.  A thread owns a
 // channel, reads entries above the one it writes, and so needs no second buffer.
 template <typename T>
-__global__ void causal_taps_state_kernel(const T* __restrict__ x, float* __restrict__ state,
+__global__ void causal_taps_state_kernel(const T* __restrict__ x, long long ldx, float* __restrict__ state,
                                          const int* __restrict__ slots, const int* __restrict__ cu_q, int C,
                                          int taps) {
     const int row = blockIdx.x;
@@ -287,7 +288,7 @@ __global__ void causal_taps_state_kernel(const T* __restrict__ x, float* __restr
     for (int c = threadIdx.x; c < C; c += blockDim.x) {
         for (int s = 0; s < taps - 1; ++s) {
             const int src = q - (taps - 1) + s;
-            st[(size_t)s * C + c] = src >= 0 ? to_f32<T>(x[(size_t)(first + src) * C + c])
+            st[(size_t)s * C + c] = src >= 0 ? to_f32<T>(x[(size_t)(first + src) * ldx + c])
                                              : st[(size_t)(s + q) * C + c];
         }
     }
@@ -296,14 +297,15 @@ __global__ void causal_taps_state_kernel(const T* __restrict__ x, float* __restr
 // A step in which every row brings one token: convolution and state in one kernel.  A thread owns
 // (row, channel), reads the state it then rewrites.
 template <typename T>
-__global__ void causal_taps_single_kernel(const T* __restrict__ x, const void* __restrict__ w, int w_dtype,
+__global__ void causal_taps_single_kernel(const T* __restrict__ x, long long ldx, const void* __restrict__ w,
+                                          int w_dtype, const void* __restrict__ bias, int identity,
                                           float* __restrict__ state, const int* __restrict__ slots,
                                           T* __restrict__ out, int C, int taps) {
     const int row = blockIdx.x;
     float* st = state + (size_t)slots[row] * (taps - 1) * C;
     for (int c = threadIdx.x; c < C; c += blockDim.x) {
-        const float h = to_f32<T>(x[(size_t)row * C + c]);
-        float conv = 0.f;
+        const float h = to_f32<T>(x[(size_t)row * ldx + c]);
+        float conv = bias ? load_any(bias, w_dtype, c) : 0.f;
         for (int j = 0; j < taps - 1; ++j) {
             const float v = st[(size_t)j * C + c];
             conv += load_any(w, w_dtype, (size_t)c * taps + j) * v;
@@ -311,7 +313,7 @@ __global__ void causal_taps_single_kernel(const T* __restrict__ x, const void* _
         }
         conv += load_any(w, w_dtype, (size_t)c * taps + taps - 1) * h;
         st[(size_t)(taps - 2) * C + c] = h;
-        out[(size_t)row * C + c] = from_f32<T>(h + conv);
+        out[(size_t)row * C + c] = from_f32<T>(identity ? h + conv : conv);
     }
 }
 
@@ -403,24 +405,27 @@ EMS_EXPORT int ems_glu_act(const void* gu, void* out, int dtype, int n, int I, i
     return launch_status();
 }
 
-EMS_EXPORT int ems_causal_taps(const void* x, const void* w, int w_dtype, void* state, const int* slots,
+EMS_EXPORT int ems_causal_taps(const void* x, long long ldx, const void* w, int w_dtype, const void* bias,
+                               int identity, void* state, const int* slots,
                                const int* cu_q, const int* row_of_token, void* out, int dtype, int n, int rows,
                                int C, int taps, cudaStream_t stream) {
     if (n <= 0) return EMS_OK;
-    if (taps < 1 || (taps > 1 && !state)) return EMS_ERR_SHAPE;
+    if (taps < 1 || (taps > 1 && !state) || ldx < C) return EMS_ERR_SHAPE;
     const int th = threads_for(C);
 #define EMS_LAUNCH_TAPS(T)                                                                                   \
     do {                                                                                                     \
         if (n == rows && taps > 1) {                                                                         \
-            causal_taps_single_kernel<T><<<rows, th, 0, stream>>>((const T*)x, w, w_dtype, (float*)state,    \
+            causal_taps_single_kernel<T><<<rows, th, 0, stream>>>((const T*)x, ldx, w, w_dtype, bias,        \
+                                                                  identity, (float*)state,                   \
                                                                   slots, (T*)out, C, taps);                  \
             break;                                                                                           \
         }                                                                                                    \
-        causal_taps_kernel<T><<<n, th, 0, stream>>>((const T*)x, w, w_dtype, (const float*)state, slots,     \
+        causal_taps_kernel<T><<<n, th, 0, stream>>>((const T*)x, ldx, w, w_dtype, bias, identity,            \
+                                                    (const float*)state, slots,                             \
                                                     cu_q, row_of_token, (T*)out, C, taps);                  \
         if (taps > 1)                                                                                        \
-            causal_taps_state_kernel<T><<<rows, th, 0, stream>>>((const T*)x, (float*)state, slots, cu_q, C, \
-                                                                 taps);                                      \
+            causal_taps_state_kernel<T><<<rows, th, 0, stream>>>((const T*)x, ldx, (float*)state, slots,     \
+                                                                 cu_q, C, taps);                             \
     } while (0)
     if (dtype == EMS_F32) EMS_LAUNCH_TAPS(float);
     else if (dtype == EMS_BF16) EMS_LAUNCH_TAPS(bf16);

@@ -75,7 +75,16 @@ def _declare(lib: ctypes.CDLL) -> None:
         "ems_stream_inject": [P, P, P, P, P, I, I, I, P],
         "ems_add_norm_grouped": [P, P, I, I, F, P, P, I, I, F, P, I, P, I, I, I, P],
         "ems_glu_act": [P, P, I, I, I, I, P],
-        "ems_causal_taps": [P, P, I, P, P, P, P, P, I, I, I, I, I, P],
+        "ems_causal_taps": [P, L, P, I, P, I, P, P, P, P, P, I, I, I, I, I, P],
+        "ems_paged_attention_masked": [P, L, P, I, P, P, P, I, I, P, P, I, I, I, I, I, I, I, P, P, L, F, I, I,
+                                       P, L, I, P],
+        "ems_unary_act": [P, P, I, L, I, P],
+        "ems_qk_prep": [P, L, I, I, I, I, I, P, P, P, I, I, I, F, P, P, P, I, I, I, I, P],
+        "ems_norm_mean2": [P, P, P, P, I, P, I, I, I, F, P],
+        "ems_matrix_recurrence": [P, L, P, L, P, L, I, I, F, P, P, P, P, F, P, P, I, I, P, P, I, I, I, I, I, P, P],
+        "ems_mlstm_gates": [P, P, P, I, F, P, I, I, P, P, I, I, P, P, P, P],
+        "ems_group_norm_gate": [P, P, P, I, P, L, P, I, I, I, I, F, P],
+        "ems_rglru_scan": [P, P, P, P, P, I, P, L, I, F, P, P, P, P, I, I, I, I, I, P],
         "ems_latent_prep": [P, I, I, I, I, I, I, P, P, I, F, P, P, P, I, I, P, P, I, I, P, I, P],
         "ems_rope_inplace": [P, I, I, I, I, I, I, I, I, P, P, P],
         "ems_latent_attention": [P, P, I, I, I, P, P, I, I, P, P, P, I, I, I, I, F, I, P, L, I, P],
@@ -325,18 +334,24 @@ def glu_act(gate_up: torch.Tensor, out: torch.Tensor, act: str) -> None:
 
 
 def causal_taps(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor | None, slots: torch.Tensor | None,
-                cu_q: torch.Tensor, row_of_token: torch.Tensor, out: torch.Tensor, num_rows: int) -> None:
-    """out[t] = x[t] + sum_j weight[:, j] * x[t - taps + 1 + j] along each request's own tokens, with
-    the inputs before the step's first token taken from `state` ([slots, taps - 1, C] float32, the
-    last taps - 1 inputs of each request in time order), which is then brought up to date."""
+                cu_q: torch.Tensor, row_of_token: torch.Tensor, out: torch.Tensor, num_rows: int,
+                bias: torch.Tensor | None = None, identity: bool = True) -> None:
+    """out[t] = (x[t] if identity) + bias + sum_j weight[:, j] * x[t - taps + 1 + j] along each request's
+    own tokens, with the inputs before the step's first token taken from `state` ([slots, taps - 1, C]
+    float32, the last taps - 1 inputs of each request in time order), which is then brought up to
+    date.  `x` may be a column range of a wider buffer."""
     n, c = x.shape
     taps = weight.shape[1]
-    assert weight.shape[0] == c and out.shape == x.shape and out.dtype == x.dtype
+    assert weight.shape[0] == c and out.shape == x.shape and out.dtype == x.dtype and x.stride(1) == 1
+    assert bias is None or (bias.numel() == c and bias.dtype == weight.dtype)
     if taps > 1:
         assert state is not None and state.dtype == torch.float32 and state.shape[1:] == (taps - 1, c)
         assert slots is not None
+    if not x.is_cuda:
+        raise KernelError("x must be a CUDA tensor (emberserve_b200 has no CPU path)")
     _check(library().ems_causal_taps(
-        _ptr(x, "x"), _ptr(weight, "weight"), _dt(weight), _ptr(state, "state"), _i32(slots, "slots"),
+        x.data_ptr(), x.stride(0), _ptr(weight, "weight"), _dt(weight), _ptr(bias, "bias"), 1 if identity else 0,
+        _ptr(state, "state"), _i32(slots, "slots"),
         _i32(cu_q, "cu_q"), _i32(row_of_token, "row_of_token"), _ptr(out, "out"), _dt(out), n, num_rows, c, taps,
         _stream()), "causal_taps", 2 if taps > 1 else 1)
 
@@ -595,6 +610,180 @@ def decode_attention_fused(qkv: torch.Tensor, out: torch.Tensor, kcache: torch.T
         _ptr(rope_table, "rope_table"), rotary_dim, 1 if write_kv else 0, splits, _ptr(scratch, "scratch"),
         0 if scratch is None else scratch.numel() * scratch.element_size(), _stream()),
         "decode_attention_fused", 2 if splits > 1 else 1)
+
+
+# ---------------------------------------------------------------------------------------
+# ungated feed-forward, prepared attention heads, masked attention, recurrent mixers
+
+UNARY_ACTIVATIONS = {"relu": 0, "relu2": 1, "gelu_tanh": 2, "silu": 3}
+
+
+def unary_act(x: torch.Tensor, out: torch.Tensor, act: str) -> None:
+    """out = act(x) elementwise for act in `UNARY_ACTIVATIONS` (relu2 is the square of relu)."""
+    assert x.shape == out.shape and x.dtype == out.dtype
+    _check(library().ems_unary_act(_ptr(x, "x"), _ptr(out, "out"), _dt(out), x.numel(), UNARY_ACTIVATIONS[act],
+                                   _stream()), "unary_act")
+
+
+def qk_prep(proj: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, positions: torch.Tensor,
+            row_of_token: torch.Tensor, table: torch.Tensor | None, rot_dims: int, pairing: str,
+            norm_eps: float | None, kcache: torch.Tensor, vcache: torch.Tensor, block_tables: torch.Tensor,
+            values_are_keys: bool, write: bool = True) -> None:
+    """The tokens of a step for attention over a paged cache.  proj: [N, >= (nh + nkv (+ nkv)) * D]
+    holds [q | k | v] per row (no v when `values_are_keys`: the value of a token is then its key as
+    projected).  Every head of q and k is rotated by the table rows of `positions` on its first
+    `rot_dims` numbers and, with `norm_eps`, divided by its root mean square; q is rewritten in
+    place, k and v go to the token's page slot.  caches: [pages, nkv, page_size, D]."""
+    n = proj.shape[0]
+    cols = (num_heads + num_kv_heads * (1 if values_are_keys else 2)) * head_dim
+    assert proj.stride(1) == 1 and proj.shape[1] >= cols
+    assert kcache.dtype == vcache.dtype == proj.dtype and kcache.shape[1] == num_kv_heads and kcache.shape[3] == head_dim
+    assert table is None or (table.dtype == torch.float32 and table.shape[1] * 2 == rot_dims)
+    if not proj.is_cuda:
+        raise KernelError("proj must be a CUDA tensor (emberserve_b200 has no CPU path)")
+    _check(library().ems_qk_prep(
+        proj.data_ptr(), proj.stride(0), _dt(proj), n, num_heads, num_kv_heads, head_dim,
+        _i32(positions, "positions"), _i32(row_of_token, "row_of_token"), _ptr(table, "table"),
+        rot_dims if table is not None else 0, ROTARY_PAIRINGS[pairing], 0 if norm_eps is None else 1,
+        float(norm_eps or 0.0), _ptr(kcache, "kcache"), _ptr(vcache, "vcache"), _i32(block_tables, "block_tables"),
+        block_tables.shape[1], kcache.shape[2], 1 if values_are_keys else 0, 1 if write else 0, _stream()), "qk_prep")
+
+
+def paged_attention_masked(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
+                           block_tables: torch.Tensor, cu_q: torch.Tensor, starts: torch.Tensor,
+                           num_rows: int, num_tokens: int, num_heads: int, num_kv_heads: int,
+                           head_dim: int, scale: float, max_q_len: int, window: int | None = None,
+                           chunk: int | None = None, sinks: torch.Tensor | None = None,
+                           gate: torch.Tensor | None = None, splits: int = 1,
+                           scratch: torch.Tensor | None = None, kernel: str = "auto") -> None:
+    """`paged_attention` with three optional extras: `chunk` (the query at position p sees key j <= p
+    only if j // chunk == p // chunk, chunks counted from position 0 of the request), `sinks`
+    (float32 [nh]: exp(sinks[h]) is added to head h's softmax denominator; it has no value) and
+    `gate` ([N, >= nh], may be a column range of a wider buffer: head h's output is multiplied by
+    sigmoid(gate[n, h]))."""
+    assert q.stride(1) == 1 and out.is_contiguous() and q.dtype == out.dtype == kcache.dtype
+    page_size = kcache.shape[2]
+    assert kcache.shape[1] == num_kv_heads and kcache.shape[3] == head_dim
+    assert sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == num_heads)
+    assert gate is None or (gate.dtype == q.dtype and gate.stride(1) == 1 and gate.shape[1] >= num_heads)
+    if not q.is_cuda:
+        raise KernelError("q must be a CUDA tensor (emberserve_b200 has no CPU path)")
+    _check(library().ems_paged_attention_masked(
+        q.data_ptr(), q.stride(0), _ptr(out, "out"), _dt(out), _ptr(kcache, "kcache"),
+        _ptr(vcache, "vcache"), _i32(block_tables, "block_tables"), block_tables.shape[1], page_size,
+        _i32(cu_q, "cu_q"), _i32(starts, "starts"), num_rows, num_tokens, num_heads, num_kv_heads,
+        head_dim, int(window or 0), int(chunk or 0), _ptr(sinks, "sinks"),
+        None if gate is None else gate.data_ptr(), 0 if gate is None else gate.stride(0), float(scale), max_q_len,
+        splits, _ptr(scratch, "scratch"), 0 if scratch is None else scratch.numel() * scratch.element_size(),
+        _ATTENTION_IMPL[kernel], _stream()), "paged_attention_masked", 2 if splits > 1 else 1)
+
+
+def norm_mean2(a: torch.Tensor, b: torch.Tensor, gain_a: torch.Tensor, gain_b: torch.Tensor, eps: float,
+               out: torch.Tensor) -> None:
+    """out = (rms(a) * gain_a + rms(b) * gain_b) / 2 over rows of equal width, statistics in 32 bits."""
+    n, c = a.shape
+    assert b.shape == out.shape == (n, c) and a.dtype == b.dtype == out.dtype
+    assert gain_a.numel() == gain_b.numel() == c and gain_a.dtype == gain_b.dtype
+    _check(library().ems_norm_mean2(_ptr(a, "a"), _ptr(b, "b"), _ptr(gain_a, "gain_a"), _ptr(gain_b, "gain_b"),
+                                    _dt(gain_a), _ptr(out, "out"), _dt(out), n, c, float(eps), _stream()),
+           "norm_mean2")
+
+
+MEMORY_INPUT_ACTIVATIONS = {"none": 0, "silu": 1}
+
+
+def _f32(t: torch.Tensor | None, name: str) -> int | None:
+    if t is not None and t.dtype != torch.float32:
+        raise KernelError(f"{name} must be float32, got {t.dtype}")
+    return _ptr(t, name)
+
+
+def matrix_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, num_heads: int, dim: int, vdim: int,
+                      state: torch.Tensor, slots: torch.Tensor, cu_q: torch.Tensor, num_rows: int,
+                      out: torch.Tensor, act: str = "none", q_scale: float = 1.0,
+                      decay_head: torch.Tensor | None = None, a: torch.Tensor | None = None,
+                      b: torch.Tensor | None = None, denom_floor: torch.Tensor | None = None,
+                      denom: torch.Tensor | None = None, denom_eps: float = 0.0) -> None:
+    """A matrix memory per head, run over every request's tokens in order:
+
+        S_t = a_t S_(t-1) + b_t k_t v_t^T,        out_t = S_t^T (q_t * q_scale)
+
+    q, k: [N, >= H * dim], v: [N, >= H * vdim] (column ranges of wider buffers are fine), each passed
+    through `act` first; a_t is `decay_head[h]` for every token or `a[t, h]`; b_t is `b[t, h]` or 1.
+    state: float32 [slots, H, per_head] holding S ([dim, vdim]) and, when `denom` is given, the
+    normaliser n_t = a_t n_(t-1) + b_t k_t ([dim]) behind it; then denom[t, h] = max(|n_t . q_t|,
+    denom_floor[t, h]) + denom_eps.  out: float32 [N, H * vdim], not yet divided."""
+    n = q.shape[0]
+    assert q.stride(1) == k.stride(1) == v.stride(1) == 1 and q.dtype == k.dtype == v.dtype
+    assert out.dtype == torch.float32 and out.shape == (n, num_heads * vdim) and state.dtype == torch.float32
+    assert state.dim() == 3 and state.shape[1] == num_heads
+    assert (decay_head is None) != (a is None)
+    if not q.is_cuda:
+        raise KernelError("q must be a CUDA tensor (emberserve_b200 has no CPU path)")
+    _check(library().ems_matrix_recurrence(
+        q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), _dt(q),
+        MEMORY_INPUT_ACTIVATIONS[act], float(q_scale), _f32(decay_head, "decay_head"), _f32(a, "a"), _f32(b, "b"),
+        _f32(denom_floor, "denom_floor"), float(denom_eps), _f32(denom, "denom"), _ptr(state, "state"),
+        state.shape[2], 0 if denom is None else 1, _i32(slots, "slots"), _i32(cu_q, "cu_q"), num_rows, n,
+        num_heads, dim, vdim, _ptr(out, "out"), _stream()), "matrix_recurrence")
+
+
+def mlstm_gates(pre: torch.Tensor, bias_i: torch.Tensor, bias_f: torch.Tensor, cap: float, state: torch.Tensor,
+                m_offset: int, slots: torch.Tensor, cu_q: torch.Tensor, num_rows: int, a: torch.Tensor,
+                b: torch.Tensor, floor: torch.Tensor) -> None:
+    """The stabilised exponential gates of an mLSTM.  pre: float32 [N, 2 H], input-gate then
+    forget-gate pre-activations.  i = cap tanh((pre_i + bias_i) / cap), f = logsigmoid(cap tanh((pre_f +
+    bias_f) / cap)); the running maximum m_t = max(f + m_(t-1), i) lives at state[slot, h, m_offset]
+    (0 in a fresh slot); a = exp(f + m_(t-1) - m_t), b = exp(i - m_t), floor = exp(-m_t), float32 [N, H]."""
+    n, h2 = pre.shape
+    h = h2 // 2
+    assert pre.dtype == torch.float32 and state.dtype == torch.float32 and state.shape[1] == h
+    assert bias_i.numel() == bias_f.numel() == h and bias_i.dtype == bias_f.dtype
+    assert a.shape == b.shape == floor.shape == (n, h)
+    _check(library().ems_mlstm_gates(
+        _f32(pre, "pre"), _ptr(bias_i, "bias_i"), _ptr(bias_f, "bias_f"), _dt(bias_i), float(cap),
+        _ptr(state, "state"), state.shape[2], m_offset, _i32(slots, "slots"), _i32(cu_q, "cu_q"), num_rows, h,
+        _f32(a, "a"), _f32(b, "b"), _f32(floor, "floor"), _stream()), "mlstm_gates")
+
+
+def group_norm_gate(o: torch.Tensor, groups: int, eps: float, weight: torch.Tensor, gate: torch.Tensor | None,
+                    out: torch.Tensor, denom: torch.Tensor | None = None) -> None:
+    """out = rms_g(o / denom) * weight * sigmoid(gate): `o` float32 [N, C] is divided per (token, group)
+    by `denom` ([N, groups], optional), each of `groups` equal consecutive parts of a row by its
+    root mean square; `gate` ([N, >= C], may be a column range) is optional."""
+    n, c = o.shape
+    assert o.dtype == torch.float32 and out.shape == (n, c) and weight.numel() == c
+    assert gate is None or (gate.dtype == out.dtype and gate.stride(1) == 1 and gate.shape[1] >= c)
+    assert denom is None or denom.shape == (n, groups)
+    if not o.is_cuda:
+        raise KernelError("o must be a CUDA tensor (emberserve_b200 has no CPU path)")
+    _check(library().ems_group_norm_gate(
+        _f32(o, "o"), _f32(denom, "denom"), _ptr(weight, "weight"), _dt(weight),
+        None if gate is None else gate.data_ptr(), 0 if gate is None else gate.stride(0), _ptr(out, "out"), _dt(out),
+        n, c, groups, float(eps), _stream()), "group_norm_gate")
+
+
+def rglru_scan(u: torch.Tensor, pre: torch.Tensor, bias_r: torch.Tensor, bias_i: torch.Tensor, lam: torch.Tensor,
+               y: torch.Tensor, y_act: bool, cmul: float, state: torch.Tensor, slots: torch.Tensor,
+               cu_q: torch.Tensor, num_rows: int, out: torch.Tensor, blocks: int) -> None:
+    """A gated diagonal recurrence per channel over every request's tokens in order:
+
+        r = sigmoid(pre_r + bias_r), i = sigmoid(pre_i + bias_i), a = exp(-cmul * r * softplus(lam)),
+        S_t = a S_(t-1) + sqrt(1 - a^2) * i * u_t,      out_t = S_t * (gelu_tanh(y_t) if y_act else y_t)
+
+    u, out: [N, C]; pre: float32 [2, blocks, N, C / blocks] (the r gates, then the i gates, block by block);
+    y: [N, >= C], may be a column range; state: float32 [slots, C]."""
+    n, c = u.shape
+    assert pre.dtype == torch.float32 and pre.numel() == 2 * n * c and state.dtype == torch.float32
+    assert state.shape[1:] == (c,) and out.shape == (n, c) and out.dtype == u.dtype == y.dtype and y.stride(1) == 1
+    assert bias_r.numel() == bias_i.numel() == lam.numel() == c and bias_r.dtype == bias_i.dtype == lam.dtype
+    if not u.is_cuda:
+        raise KernelError("u must be a CUDA tensor (emberserve_b200 has no CPU path)")
+    _check(library().ems_rglru_scan(
+        _ptr(u, "u"), _f32(pre, "pre"), _ptr(bias_r, "bias_r"), _ptr(bias_i, "bias_i"), _ptr(lam, "lam"),
+        _dt(lam), y.data_ptr(), y.stride(0), 1 if y_act else 0, float(cmul), _ptr(state, "state"),
+        _i32(slots, "slots"), _i32(cu_q, "cu_q"), _ptr(out, "out"), _dt(out), num_rows, n, c, blocks, _stream()),
+        "rglru_scan")
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:

@@ -1,6 +1,7 @@
 """Parts a decoder is assembled from.  Importing the package registers the built-in kinds."""
 
-from emberserve_b200.parts import attention, block, conv, latent_attention, mlp, moe, norm, rope  # noqa: F401
+from emberserve_b200.parts import (attention, block, conv, latent_attention, mlp, moe, norm, parallel,  # noqa: F401
+                                   recurrent, rope, sink_attention)
 from emberserve_b200.parts.base import (Block, FeedForward, FixedState, FixedStateHandle, Mixer,
                                         Norm, PagedKV, PagedKVHandle, ParamSpec, Part,
                                         PositionEncoding, Source, StepContext, build_part,

@@ -57,11 +57,14 @@ class ParamSpec:
 @dataclass(frozen=True)
 class PagedKV:
     """Keys and values of every token, in pages.  `window`: only the last `window`
-    keys are ever read again (None = all), so older pages may be given back."""
+    keys are ever read again (None = all), so older pages may be given back.  `chunk`: a query
+    reads only keys of its own chunk of `chunk` positions (chunks counted from position 0), so
+    pages that lie wholly before the chunk of the next position may be given back."""
 
     num_kv_heads: int
     head_dim: int
     window: int | None = None
+    chunk: int | None = None
 
     paged = True
 
@@ -107,6 +110,7 @@ class PagedKVHandle:
     page_size: int
     window: int | None
     write: bool  # False: read what another layer call wrote in this step
+    chunk: int | None = None
 
 
 @dataclass

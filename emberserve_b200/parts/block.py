@@ -1,6 +1,6 @@
 """Residual blocks.
 
-Pre-norm: ``h += mixer(norm1(h)); h += ffn(norm2(h))``.
+Pre-norm: ``h += mixer(norm1(h)); h += ffn(norm2(h))`` (a layer without a feed-forward is its first half).
 Sandwich (a norm before AND behind every sub-layer, optionally a short convolution before the
 mixer, optionally no feed-forward): ``h += norm1b(mixer(conv(norm1(h)))); h += norm2b(ffn(norm2(h)))``.
 
@@ -23,7 +23,7 @@ from emberserve_b200.parts.base import (Block, CacheNeed, NormedDelta, Part, Ste
 @dataclass(frozen=True)
 class PreNormBlockSpec:
     mixer: Any
-    feed_forward: Any
+    feed_forward: Any  # None: the block is its mixer alone
     mixer_norm: Any
     ffn_norm: Any
     kind: str = "prenorm"
@@ -35,12 +35,16 @@ class PreNormBlock(Block):
         super().__init__(spec, prefix, shared)
         self.mixer_norm = build_part("norm", spec.mixer_norm, prefix + ".mixer_norm", self.shared)
         self.mixer = build_part("mixer", spec.mixer, prefix + ".mixer", self.shared)
-        self.ffn_norm = build_part("norm", spec.ffn_norm, prefix + ".ffn_norm", self.shared)
-        self.ffn = build_part("feed_forward", spec.feed_forward, prefix + ".ffn", self.shared)
+        self.ffn = self.ffn_norm = None
+        if spec.feed_forward is not None:
+            self.ffn_norm = build_part("norm", spec.ffn_norm, prefix + ".ffn_norm", self.shared)
+            self.ffn = build_part("feed_forward", spec.feed_forward, prefix + ".ffn", self.shared)
 
     def children(self) -> dict[str, Part]:
-        return {"mixer_norm": self.mixer_norm, "mixer": self.mixer,
-                "ffn_norm": self.ffn_norm, "ffn": self.ffn}
+        out = {"mixer_norm": self.mixer_norm, "mixer": self.mixer}
+        if self.ffn is not None:
+            out.update(ffn_norm=self.ffn_norm, ffn=self.ffn)
+        return out
 
     def cache_need(self) -> CacheNeed | None:
         return self.mixer.cache_need()
@@ -54,6 +58,12 @@ class PreNormBlock(Block):
         # it in its last product (ctx.extra["norm_behind"]); what it returns says whether it did.
         after_ffn = ctx.extra.pop("next_norm", None)  # the next block's entry norm, from the decoder
         x = self.mixer_norm.forward(delta, residual, ctx)
+        if self.ffn is None:
+            ctx.extra["norm_behind"] = (after_ffn.split_request(residual, ctx)
+                                        if after_ffn is not None and self.mixer.splits_norms else None)
+            a = self.mixer.forward(x, ctx, cache)
+            ctx.extra["norm_behind"] = None
+            return a
         ctx.extra["norm_behind"] = (self.ffn_norm.split_request(residual, ctx)
                                     if self.mixer.splits_norms and self.ffn.splits_norms else None)
         a = self.mixer.forward(x, ctx, cache)

@@ -1,7 +1,7 @@
-"""A short causal convolution over time on every channel, added to its input:
+"""A short causal convolution over time on every channel, by default added to its input:
 
 ``out[t] = h[t] + sum_j w[:, j] * h[t - taps + 1 + j]`` with ``h = 0`` before a request's
-first token.  The last ``taps - 1`` inputs of a request are state that lives between steps
+first token; with ``identity=False`` the input itself is not added, and a bias per channel may be.  The last ``taps - 1`` inputs of a request are state that lives between steps
 (``FixedState((taps - 1, width))``, float32), so a portion of a prompt or a single decoded
 token continues where the step before stopped.  A block puts it between a norm and a mixer.
 """
@@ -23,11 +23,14 @@ class CausalTapsSpec:
     taps: int
     weight_name: str  # checkpoint tensor [width, taps]; column taps - 1 multiplies the current input
     kind: str = "causal_taps"
+    identity: bool = True  # add the input to the convolution's output
+    bias_name: str | None = None  # checkpoint tensor [width]
 
 
 @register_part("conv", "causal_taps")
 class CausalTaps(Part):
     weight: torch.Tensor
+    bias: torch.Tensor | None = None
 
     def __init__(self, spec: CausalTapsSpec, prefix: str, shared=None) -> None:
         super().__init__(spec, prefix, shared)
@@ -36,7 +39,10 @@ class CausalTaps(Part):
 
     def param_specs(self) -> dict[str, ParamSpec]:
         s: CausalTapsSpec = self.spec
-        return {"weight": ParamSpec((s.width, s.taps), [Source(s.weight_name)])}
+        specs = {"weight": ParamSpec((s.width, s.taps), [Source(s.weight_name)])}
+        if s.bias_name is not None:
+            specs["bias"] = ParamSpec((s.width,), [Source(s.bias_name)], init="bias")
+        return specs
 
     def cache_need(self) -> FixedState | None:
         s: CausalTapsSpec = self.spec
@@ -49,5 +55,6 @@ class CausalTaps(Part):
         s: CausalTapsSpec = self.spec
         out = ctx.scratch("taps_out", (ctx.num_tokens, s.width), ctx.dtype)
         K.causal_taps(x, self.weight, None if cache is None else cache.state,
-                      None if cache is None else cache.slots, ctx.cu_q, ctx.row_of_token, out, ctx.num_rows)
+                      None if cache is None else cache.slots, ctx.cu_q, ctx.row_of_token, out, ctx.num_rows,
+                      bias=self.bias, identity=s.identity)
         return out

@@ -239,3 +239,27 @@ def linear_f32_out(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> 
         return out
     out.copy_(torch.mm(x.float(), weight.float().t()))
     return out
+
+
+_BMM_F32_OUT_OK: bool | None = None
+
+
+def bmm_f32_out(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out (float32, [B, N, M]) = a @ b per batch entry, accumulated in float32 and never rounded to
+    the activation type (gate pre-activations of a recurrence).  a: [B, N, K], b: [B, K, M]; both may
+    be strided views."""
+    global _BMM_F32_OUT_OK
+    if a.dtype == torch.float32 and b.dtype == torch.float32:
+        torch.bmm(a, b, out=out)
+        return out
+    if a.dtype == b.dtype == torch.bfloat16 and a.is_cuda and _BMM_F32_OUT_OK is not False:
+        try:
+            torch.bmm(a, b, out_dtype=torch.float32, out=out)
+            _BMM_F32_OUT_OK = True
+            return out
+        except (TypeError, RuntimeError):
+            if _BMM_F32_OUT_OK:
+                raise
+            _BMM_F32_OUT_OK = False
+    torch.bmm(a.float(), b.float(), out=out)
+    return out

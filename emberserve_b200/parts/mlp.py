@@ -1,5 +1,7 @@
-"""Dense gated feed-forward: ``down(act(gate(x)) * up(x))``, no biases; act is SiLU (SwiGLU)
+"""Dense feed-forwards.  Gated: ``down(act(gate(x)) * up(x))``, no biases; act is SiLU (SwiGLU)
 unless the spec names another (``relu``, ``gelu_tanh``), which takes the unfused kernels.
+Ungated (``DenseMLP``): ``down(act(up(x)))`` with act one of ``kernels.UNARY_ACTIVATIONS``
+(``relu2`` is the square of relu).
 
 gate and up are one fused projection whose first I output columns are the gate and the
 last I the up part (``emberserve/model/qwen2.py:48-61``); the activation is
@@ -72,3 +74,48 @@ class SwiGLU(FeedForward):
         y = ctx.scratch("ffn_out", (n, s.hidden), ctx.dtype)
         # (the norm behind this feed-forward, if the down projection's product may begin it)
         return linear(act, self.wdown, None, y, ctx.scratch, ctx.extra.get("norm_behind"))
+
+
+@dataclass(frozen=True)
+class DenseMLPSpec:
+    hidden: int
+    intermediate: int
+    up_name: str  # checkpoint tensor [intermediate, hidden]
+    down_name: str  # checkpoint tensor [hidden, intermediate]
+    activation: str = "relu2"  # one of kernels.UNARY_ACTIVATIONS
+    kind: str = "dense_mlp"
+
+
+@register_part("feed_forward", "dense_mlp")
+class DenseMLP(FeedForward):
+    """``down(act(up(x)))`` without gate and without biases; the activation is computed in 32 bits
+    from the rounded projection and rounded once."""
+
+    wup: torch.Tensor
+    wdown: torch.Tensor
+
+    def __init__(self, spec: DenseMLPSpec, prefix: str, shared=None) -> None:
+        super().__init__(spec, prefix, shared)
+        if spec.activation not in K.UNARY_ACTIVATIONS:
+            raise ValueError(f"activation {spec.activation!r}: one of {sorted(K.UNARY_ACTIVATIONS)}")
+
+    def param_specs(self) -> dict[str, ParamSpec]:
+        s: DenseMLPSpec = self.spec
+        return {"wup": ParamSpec((s.intermediate, s.hidden), [Source(s.up_name)]),
+                "wdown": ParamSpec((s.hidden, s.intermediate), [Source(s.down_name)])}
+
+    def streamed_params(self) -> list[str]:
+        return ["wup", "wdown"]
+
+    def scratch_elements_per_token(self) -> int:
+        return 2 * self.spec.intermediate + self.spec.hidden
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        s: DenseMLPSpec = self.spec
+        n = x.shape[0]
+        up = ctx.scratch("ffn_up", (n, s.intermediate), ctx.dtype)
+        linear(x, self.wup, None, up, ctx.scratch)
+        act = ctx.scratch("ffn_act", (n, s.intermediate), ctx.dtype)
+        K.unary_act(up, act, s.activation)
+        y = ctx.scratch("ffn_out", (n, s.hidden), ctx.dtype)
+        return linear(act, self.wdown, None, y, ctx.scratch)

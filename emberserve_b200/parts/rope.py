@@ -10,6 +10,7 @@ keys and values into the cache (``csrc/elementwise.cu``).
 
 from __future__ import annotations
 
+import math
 from dataclasses import dataclass
 
 import torch
@@ -68,3 +69,60 @@ class RotaryInterleaved(RotaryNeox):
     turns is (2i, 2i + 1)."""
 
     pairing = "interleaved"
+
+
+@dataclass(frozen=True)
+class RotaryYarnSpec:
+    """Rotary angles whose slow pairs are stretched by `factor` (YaRN: Peng et al., "YaRN: Efficient
+    Context Window Extension of Large Language Models").  With ``where(t) = rotary_dim * ln(original /
+    (2 pi t)) / (2 ln theta)``, pairs below ``lo = max(floor(where(fast)), 0)`` keep their frequency,
+    pairs above ``hi = min(ceil(where(slow)), rotary_dim - 1)`` are divided by `factor`, and those
+    between are blended linearly; cos and sin are both multiplied by ``0.1 ln(factor) + 1``."""
+
+    rotary_dim: int
+    theta: float
+    max_positions: int
+    factor: float
+    original: int
+    fast: float
+    slow: float
+    pairing: str = "interleaved"  # or "half"
+    kind: str = "rotary_yarn"
+
+
+def yarn_inv_frequencies(s: RotaryYarnSpec) -> tuple[torch.Tensor, float]:
+    """(float32 frequency of every pair, the factor on cos and sin); computed in 64 bits, rounded once."""
+    half = s.rotary_dim // 2
+    i = torch.arange(half, dtype=torch.float64)
+    f = float(s.theta) ** (-2.0 * i / s.rotary_dim)
+
+    def where(turns: float) -> float:
+        return s.rotary_dim * math.log(s.original / (2 * math.pi * turns)) / (2 * math.log(s.theta))
+
+    lo = max(math.floor(where(s.fast)), 0)
+    hi = min(math.ceil(where(s.slow)), s.rotary_dim - 1)
+    ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0, 1)
+    return (f / s.factor * ramp + f * (1 - ramp)).to(torch.float32), 0.1 * math.log(s.factor) + 1.0
+
+
+@register_part("position", "rotary_yarn")
+class RotaryYarn(RotaryNeox):
+    """The table holds ``mag * cos`` and ``mag * sin`` of ``pos * frequency[i]``, so the kernels that
+    rotate by a table need not know about the scaling."""
+
+    def __init__(self, spec: RotaryYarnSpec, prefix: str, shared=None) -> None:
+        super().__init__(spec, prefix, shared)
+        if spec.pairing not in K.ROTARY_PAIRINGS:
+            raise ValueError(f"pairing {spec.pairing!r}: one of {sorted(K.ROTARY_PAIRINGS)}")
+        if min(spec.factor, spec.original, spec.fast, spec.slow) <= 0 or spec.theta <= 1:
+            raise ValueError("YaRN scaling needs positive factor, original, fast and slow and a base above 1")
+        self.pairing = spec.pairing
+
+    def rotary(self, device: torch.device) -> tuple[torch.Tensor, int]:
+        s: RotaryYarnSpec = self.spec
+        if self._table is None or self._table.device != device:
+            inv, mag = yarn_inv_frequencies(s)
+            self._table = K.rope_table(inv.to(device), s.max_positions)
+            if mag != 1.0:
+                self._table.mul_(mag)
+        return self._table, s.rotary_dim

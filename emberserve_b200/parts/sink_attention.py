@@ -1,0 +1,145 @@
+"""Grouped-query attention over a paged cache with the options that newer decoders combine:
+
+* the values may be the keys themselves as projected, before rotation and norm (no value projection);
+* q and k, after a rotation of the first `rotary_dim` numbers of each head, may be divided by
+  their root mean square per head (a norm without gain);
+* a chunk mask: the query at position p sees key j <= p only if ``j // chunk == p // chunk``,
+  chunks counted from position 0 of the request, wherever a prompt was cut; and / or a window;
+* a sink: ``exp(sink[h])`` joins the softmax denominator of head h; it has no key and no value;
+* a gate per (token, head): head h's output is multiplied by ``sigmoid(x Wg^T)[h]``.
+
+``[q | k | (v) | gate] = x W^T + b`` is one product; one kernel rotates, norms and writes the
+cache; the attention kernel applies mask, sink and gate; then ``o = attn Wo^T``.  Scores, softmax,
+rotation and the unit norms are 32-bit.  With a chunk mask the cache gives back the pages of
+chunks that are over (``PagedKV.chunk``).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any
+
+import torch
+
+from emberserve_b200 import kernels as K
+from emberserve_b200.parts.attention import decode_splits
+from emberserve_b200.parts.base import (Mixer, PagedKV, PagedKVHandle, ParamSpec, Source, StepContext,
+                                        register_part)
+from emberserve_b200.parts.linear import linear
+
+
+@dataclass(frozen=True)
+class SinkAttentionSpec:
+    hidden: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    scale: float
+    position: Any  # spec of a rotary position encoding, or None
+    # checkpoint tensors (full names); a bias name may be None
+    q_name: str
+    k_name: str
+    o_name: str
+    v_name: str | None = None  # None: the values are the keys as projected
+    q_bias_name: str | None = None
+    k_bias_name: str | None = None
+    v_bias_name: str | None = None
+    sink_name: str | None = None  # [num_heads]
+    gate_name: str | None = None  # [num_heads, hidden]
+    qk_norm_eps: float | None = None  # unit RMS of q and k per head after the rotation
+    chunk: int | None = None
+    window: int | None = None
+    kind: str = "sink_attention"
+
+
+@register_part("mixer", "sink_attention")
+class SinkAttention(Mixer):
+    wqkv: torch.Tensor
+    wo: torch.Tensor
+    bqkv: torch.Tensor | None = None
+    sink: torch.Tensor | None = None
+
+    def __init__(self, spec: SinkAttentionSpec, prefix: str, shared=None) -> None:
+        super().__init__(spec, prefix, shared)
+        if spec.num_heads % spec.num_kv_heads:
+            raise ValueError("num_heads must be a multiple of num_kv_heads")
+        if spec.head_dim % 8 or spec.head_dim > 256:
+            raise ValueError(f"head_dim={spec.head_dim}: the attention kernels take multiples of 8 up to 256")
+        self.q_size = spec.num_heads * spec.head_dim
+        self.kv_size = spec.num_kv_heads * spec.head_dim
+        self.v_cols = 0 if spec.v_name is None else self.kv_size
+        self.gate_at = self.q_size + self.kv_size + self.v_cols
+        # the gate's columns are padded so that a row of the product stays 16-byte aligned
+        self.gate_cols = 0 if spec.gate_name is None else -(-spec.num_heads // 8) * 8
+        self.cols = self.gate_at + self.gate_cols
+        self.position = self.shared.get("position", spec.position) if spec.position is not None else None
+        self._sink32: torch.Tensor | None = None
+
+    def cache_need(self) -> PagedKV:
+        s: SinkAttentionSpec = self.spec
+        return PagedKV(s.num_kv_heads, s.head_dim, s.window, s.chunk)
+
+    def param_specs(self) -> dict[str, ParamSpec]:
+        s: SinkAttentionSpec = self.spec
+        q, kv = self.q_size, self.kv_size
+        rows = [(s.q_name, s.q_bias_name, (0, q)), (s.k_name, s.k_bias_name, (q, q + kv))]
+        if s.v_name is not None:
+            rows.append((s.v_name, s.v_bias_name, (q + kv, q + 2 * kv)))
+        if s.gate_name is not None:
+            rows.append((s.gate_name, None, (self.gate_at, self.gate_at + s.num_heads)))
+        # (rows that no tensor fills, the gate's padding and absent biases, stay zero)
+        specs = {
+            "wqkv": ParamSpec((self.cols, s.hidden), [Source(n, r) for n, _, r in rows]),
+            "wo": ParamSpec((s.hidden, q), [Source(s.o_name)]),
+        }
+        biased = [(b, r) for _, b, r in rows if b is not None]
+        if biased:
+            specs["bqkv"] = ParamSpec((self.cols,), [Source(b, r) for b, r in biased], init="bias")
+        if s.sink_name is not None:
+            specs["sink"] = ParamSpec((s.num_heads,), [Source(s.sink_name)], init="bias")
+        return specs
+
+    def bind(self, params: dict[str, torch.Tensor]) -> None:
+        super().bind(params)
+        self._sink32 = None if self.sink is None else self.sink.float().contiguous()
+
+    def streamed_params(self) -> list[str]:
+        return ["wqkv", "wo"]
+
+    def scratch_elements_per_token(self) -> int:
+        return self.cols + self.q_size + self.spec.hidden
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: PagedKVHandle) -> torch.Tensor:
+        s: SinkAttentionSpec = self.spec
+        n, b = ctx.num_tokens, ctx.num_rows
+        proj = ctx.scratch("sink_qkv", (n, self.cols), ctx.dtype)
+        linear(x, self.wqkv, self.bqkv, proj, ctx.scratch)
+        table, rot, pairing = None, 0, "half"
+        if self.position is not None:
+            r = self.position.rotary(ctx.device)
+            if r is not None:
+                (table, rot), pairing = r, self.position.pairing
+        K.qk_prep(proj, s.num_heads, s.num_kv_heads, s.head_dim, ctx.positions, ctx.row_of_token, table, rot,
+                  pairing, s.qk_norm_eps, cache.k, cache.v, cache.block_tables, s.v_name is None, cache.write)
+        out = ctx.scratch("attn_out", (n, self.q_size), ctx.dtype)
+        gate = proj[:, self.gate_at:self.gate_at + self.gate_cols] if self.gate_cols else None
+        kern = ctx.extra.get("attn_kernel", "auto")
+        if ctx.all_decode and n == b:
+            # one token per row: the keys of a row are split over blocks when rows are few.  A chunk
+            # or a window bounds the keys a query reads, whatever the context.
+            reach = min(x for x in (ctx.max_ctx_len, s.chunk, s.window) if x)
+            splits = decode_splits(b, s.num_kv_heads, reach, K.sm_count(ctx.device))
+            scratch = None
+            if splits > 1:
+                nbytes = K.attention_scratch_bytes(b, s.num_heads, s.head_dim, splits)
+                scratch = ctx.scratch("attn_partials", (nbytes // 4,), torch.float32)
+            K.paged_attention_masked(proj, out, cache.k, cache.v, cache.block_tables, ctx.cu_q, ctx.starts, b, n,
+                                     s.num_heads, s.num_kv_heads, s.head_dim, s.scale, 1, window=s.window,
+                                     chunk=s.chunk, sinks=self._sink32, gate=gate, splits=splits, scratch=scratch,
+                                     kernel=kern)
+        else:
+            K.paged_attention_masked(proj, out, cache.k, cache.v, cache.block_tables, ctx.cu_q, ctx.starts, b, n,
+                                     s.num_heads, s.num_kv_heads, s.head_dim, s.scale, ctx.max_q_len,
+                                     window=s.window, chunk=s.chunk, sinks=self._sink32, gate=gate, kernel=kern)
+        y = ctx.scratch("mixer_out", (n, s.hidden), ctx.dtype)
+        return linear(out, self.wo, None, y, ctx.scratch)

@@ -62,6 +62,22 @@ def _source_shape(spec: ParamSpec, rows: tuple[int, int] | None) -> tuple[int, .
     return (rows[1] - rows[0], *spec.shape[1:])
 
 
+def _covers(spec: ParamSpec) -> bool:
+    """Whether the sources fill every row of the parameter."""
+    if any(src.rows is None for src in spec.sources):
+        return True
+    return sum(hi - lo for lo, hi in (src.rows for src in spec.sources)) >= spec.shape[0]
+
+
+def _zero_uncovered(param: torch.Tensor, spec: ParamSpec) -> None:
+    if _covers(spec):
+        return
+    keep = torch.zeros(spec.shape[0], dtype=torch.bool)
+    for src in spec.sources:
+        keep[src.rows[0]:src.rows[1]] = True
+    param[(~keep).to(param.device)] = 0
+
+
 def _is_wide(dtype: torch.dtype) -> bool:
     return dtype in (torch.float32, torch.float64)
 
@@ -109,7 +125,8 @@ def load_weights(decoder: Decoder, model_dir: str | os.PathLike, device: str | t
     for path, spec in table.items():
         stored = [index[s.name][1].dtype for s in spec.sources]
         target = _param_dtype(spec, stored, dtype)
-        param = torch.empty(spec.shape, dtype=target, device=device)
+        # (rows that no tensor fills, padding of a fused parameter or an absent bias, are zero)
+        param = (torch.empty if _covers(spec) else torch.zeros)(spec.shape, dtype=target, device=device)
         for src in spec.sources:
             f, _ = index[src.name]
             view = param if src.rows is None else param[src.rows[0]:src.rows[1]]
@@ -213,6 +230,7 @@ def init_random_on_device(decoder: Decoder, seed: int, device: str | torch.devic
                 hi = min(rows, lo + step)
                 p[lo:hi] = torch.randn(p[lo:hi].shape, generator=gen, device=device,
                                        dtype=torch.float32) * dev
+            _zero_uncovered(p, spec)
             params[path] = p
     decoder.bind(params)
     return params

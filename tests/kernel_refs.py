@@ -260,7 +260,7 @@ def glu_act(gate_up, out, act):
     out.copy_((_glu_activation(g, act) * u).to(out.dtype))
 
 
-def causal_taps(x, weight, state, slots, cu_q, row_of_token, out, num_rows):
+def causal_taps(x, weight, state, slots, cu_q, row_of_token, out, num_rows, bias=None, identity=True):
     taps = weight.shape[1]
     cu = cu_q.tolist()
     w = weight.float()
@@ -277,7 +277,9 @@ def causal_taps(x, weight, state, slots, cu_q, row_of_token, out, num_rows):
         conv = torch.zeros_like(h)
         for j in range(taps):
             conv += w[:, j] * full[j:j + h.shape[0]]
-        out[q0:q1] = (h + conv).to(out.dtype)
+        if bias is not None:
+            conv = conv + bias.float()
+        out[q0:q1] = ((h + conv) if identity else conv).to(out.dtype)
         if taps > 1:
             state[slot] = full[-(taps - 1):]
 
@@ -410,11 +412,175 @@ def moe_combine(y, weights, out, top):
     out.copy_((y[:n * top].view(n, top, h) * weights.view(-1)[:n * top].view(n, top, 1)).sum(1).to(out.dtype))
 
 
+def unary_act(x, out, act):
+    z = x.float()
+    if act == "relu":
+        y = torch.relu(z)
+    elif act == "relu2":
+        y = torch.relu(z) ** 2
+    elif act == "gelu_tanh":
+        y = 0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3)))
+    else:
+        y = z / (1 + torch.exp(-z))
+    out.copy_(y.to(out.dtype))
+
+
+def qk_prep(proj, num_heads, num_kv_heads, head_dim, positions, row_of_token, table, rot_dims, pairing, norm_eps,
+            kcache, vcache, block_tables, values_are_keys, write=True):
+    n, d = proj.shape[0], head_dim
+    nq, nk = num_heads * d, num_kv_heads * d
+    pos = positions[:n].long()
+    q = proj[:, :nq].float().view(n, num_heads, d)
+    k_raw = proj[:, nq:nq + nk]
+    k = k_raw.float().view(n, num_kv_heads, d)
+    v = k_raw if values_are_keys else proj[:, nq + nk:nq + 2 * nk]
+    if table is not None and rot_dims:
+        cs = table[pos][:, None]
+        q, k = _rotate_pairs(q, cs, rot_dims, pairing), _rotate_pairs(k, cs, rot_dims, pairing)
+    if norm_eps is not None:
+        q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + norm_eps)
+        k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + norm_eps)
+    vv = v.reshape(n, num_kv_heads, d).clone()
+    proj[:, :nq] = q.reshape(n, nq).to(proj.dtype)
+    if not write:
+        return
+    page_size = kcache.shape[2]
+    page = block_tables[row_of_token[:n].long(), pos // page_size].long()
+    kcache[page, :, pos % page_size, :] = k.to(kcache.dtype)
+    vcache[page, :, pos % page_size, :] = vv.to(vcache.dtype)
+
+
+def paged_attention_masked(q, out, kcache, vcache, block_tables, cu_q, starts, num_rows, num_tokens, num_heads,
+                           num_kv_heads, head_dim, scale, max_q_len, window=None, chunk=None, sinks=None, gate=None,
+                           splits=1, scratch=None, kernel="auto"):
+    page_size = kcache.shape[2]
+    groups = num_heads // num_kv_heads
+    cu, st = cu_q.tolist(), starts.tolist()
+    for b in range(num_rows):
+        q0, q1 = cu[b], cu[b + 1]
+        qlen, ctx = q1 - q0, st[b] + (q1 - q0)
+        if qlen == 0:
+            continue
+        lo = 0
+        if window:
+            lo = max(lo, st[b] - window + 1)
+        if chunk:
+            lo = max(lo, (st[b] // chunk) * chunk)
+        keys = torch.arange(lo, ctx)
+        pages = block_tables[b, keys // page_size].long()
+        k = kcache[pages, :, keys % page_size, :].float().repeat_interleave(groups, dim=1).permute(1, 0, 2)
+        v = vcache[pages, :, keys % page_size, :].float().repeat_interleave(groups, dim=1).permute(1, 0, 2)
+        qq = q[q0:q1, : num_heads * head_dim].float().view(qlen, num_heads, head_dim).permute(1, 0, 2)
+        scores = torch.matmul(qq, k.transpose(-1, -2)) * scale  # [H, qlen, T]
+        qpos = torch.arange(st[b], ctx)[:, None]
+        hidden = keys[None, :] > qpos
+        if window:
+            hidden = hidden | (keys[None, :] <= qpos - window)
+        if chunk:
+            hidden = hidden | (keys[None, :] // chunk != qpos // chunk)
+        scores = scores.masked_fill(hidden, float("-inf"))
+        mx = scores.max(-1, keepdim=True).values
+        e = torch.exp(scores - mx)
+        den = e.sum(-1, keepdim=True)
+        if sinks is not None:
+            den = den + torch.exp(sinks.float()[:, None, None] - mx)
+        o = torch.matmul(e / den, v).permute(1, 0, 2)  # [qlen, H, D]
+        if gate is not None:
+            o = o * torch.sigmoid(gate[q0:q1, :num_heads].float())[:, :, None]
+        out[q0:q1] = o.reshape(qlen, num_heads * head_dim).to(out.dtype)
+
+
+def norm_mean2(a, b, gain_a, gain_b, eps, out):
+    x, y = a.float(), b.float()
+    x = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * gain_a.float()
+    y = y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + eps) * gain_b.float()
+    out.copy_((0.5 * (x + y)).to(out.dtype))
+
+
+def _memory_act(z, act):
+    return z * torch.sigmoid(z) if act == "silu" else z
+
+
+def matrix_recurrence(q, k, v, num_heads, dim, vdim, state, slots, cu_q, num_rows, out, act="none", q_scale=1.0,
+                      decay_head=None, a=None, b=None, denom_floor=None, denom=None, denom_eps=0.0):
+    n, H, D, V = q.shape[0], num_heads, dim, vdim
+    qq = _memory_act(q[:, :H * D].float(), act).view(n, H, D) * q_scale
+    kk = _memory_act(k[:, :H * D].float(), act).view(n, H, D)
+    vv = _memory_act(v[:, :H * V].float(), act).view(n, H, V)
+    cu = cu_q.tolist()
+    for r in range(num_rows):
+        slot = int(slots[r])
+        S = state[slot, :, :D * V].reshape(H, D, V).clone()
+        nrm = state[slot, :, D * V:D * V + D].clone() if denom is not None else None
+        for t in range(cu[r], cu[r + 1]):
+            at = decay_head if decay_head is not None else a[t]
+            bt = b[t] if b is not None else torch.ones(H)
+            S = at[:, None, None] * S + bt[:, None, None] * kk[t][:, :, None] * vv[t][:, None, :]
+            out[t] = torch.einsum("hdv,hd->hv", S, qq[t]).reshape(-1)
+            if denom is not None:
+                nrm = at[:, None] * nrm + bt[:, None] * kk[t]
+                denom[t] = torch.maximum((nrm * qq[t]).sum(-1).abs(), denom_floor[t]) + denom_eps
+        state[slot, :, :D * V] = S.reshape(H, D * V)
+        if denom is not None:
+            state[slot, :, D * V:D * V + D] = nrm
+
+
+def mlstm_gates(pre, bias_i, bias_f, cap, state, m_offset, slots, cu_q, num_rows, a, b, floor):
+    H = pre.shape[1] // 2
+    ig = cap * torch.tanh((pre[:, :H] + bias_i.float()) / cap)
+    fg = torch.nn.functional.logsigmoid(cap * torch.tanh((pre[:, H:] + bias_f.float()) / cap))
+    cu = cu_q.tolist()
+    for r in range(num_rows):
+        slot = int(slots[r])
+        m = state[slot, :, m_offset].clone()
+        for t in range(cu[r], cu[r + 1]):
+            new = torch.maximum(fg[t] + m, ig[t])
+            a[t] = torch.exp(fg[t] + m - new)
+            b[t] = torch.exp(ig[t] - new)
+            floor[t] = torch.exp(-new)
+            m = new
+        state[slot, :, m_offset] = m
+
+
+def group_norm_gate(o, groups, eps, weight, gate, out, denom=None):
+    n, c = o.shape
+    x = o.view(n, groups, c // groups)
+    if denom is not None:
+        x = x / denom[:, :, None]
+    x = (x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)).reshape(n, c) * weight.float()
+    if gate is not None:
+        x = x * torch.sigmoid(gate[:, :c].float())
+    out.copy_(x.to(out.dtype))
+
+
+def rglru_scan(u, pre, bias_r, bias_i, lam, y, y_act, cmul, state, slots, cu_q, num_rows, out, blocks):
+    n, c = u.shape
+    bw = c // blocks
+    gates = pre.reshape(2, blocks, n, bw).permute(0, 2, 1, 3).reshape(2, n, c)
+    r = torch.sigmoid(gates[0] + bias_r.float().reshape(-1))
+    i = torch.sigmoid(gates[1] + bias_i.float().reshape(-1))
+    log_a = -cmul * r * torch.nn.functional.softplus(lam.float())
+    a = torch.exp(log_a)
+    x = torch.sqrt(-torch.expm1(2 * log_a)) * i * u.float()
+    yy = y[:, :c].float()
+    if y_act:
+        yy = 0.5 * yy * (1 + torch.tanh(math.sqrt(2 / math.pi) * (yy + 0.044715 * yy ** 3)))
+    cu = cu_q.tolist()
+    for row in range(num_rows):
+        slot = int(slots[row])
+        S = state[slot].clone()
+        for t in range(cu[row], cu[row + 1]):
+            S = a[t] * S + x[t]
+            out[t] = (S * yy[t]).to(out.dtype)
+        state[slot] = S
+
+
 ALL = ["gemm_smallm", "gemm_smallm_gated", "check_status", "embedding", "add_rmsnorm", "silu_mul", "rope_table", "rope_kv_write",
        "attention_scratch_bytes", "paged_attention", "argmax", "repetition_penalty", "sample",
        "stream_inject", "add_norm_grouped", "glu_act", "causal_taps", "latent_prep", "rope_inplace",
        "latent_attention_scratch_bytes", "latent_attention", "heads_gate", "moe_tile_rows", "moe_max_tiles",
-       "moe_route", "moe_up", "moe_down", "moe_combine"]
+       "moe_route", "moe_up", "moe_down", "moe_combine", "unary_act", "qk_prep", "paged_attention_masked",
+       "norm_mean2", "matrix_recurrence", "mlstm_gates", "group_norm_gate", "rglru_scan"]
 
 
 def install(monkeypatch) -> None:
