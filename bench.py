@@ -924,16 +924,9 @@ def damolorn_config(size: str, vocab: int = 32000) -> dict:
 
 
 def run_damolorn(args) -> dict:
-    import torch
-
-    from emberserve_b200 import kernels as K
     from emberserve_b200.config.damolorn import DamolornConfig
     from emberserve_b200.config.model import Qwen2Config
-    from emberserve_b200.engine.runner import ModelRunner, StepRow
 
-    assert torch.cuda.is_available(), "bench.py needs a CUDA GPU"
-    peaks = measured_peaks()
-    K.library()
     z = DAMOLORN_SIZES[args.damolorn_size]
     dam = DamolornConfig.from_dict(damolorn_config(args.damolorn_size))
     runs = len(dam.layer_runs())
@@ -941,6 +934,67 @@ def run_damolorn(args) -> dict:
         SHAPE_7B, vocab_size=32000, hidden_size=z["width"], num_attention_heads=z["heads"],
         num_key_value_heads=max(1, z["heads"] // 8), head_dim=128, intermediate_size=z["top"] * z["ff"],
         num_hidden_layers=runs, max_position_embeddings=8192, architectures=["Qwen2ForCausalLM"], model_type="qwen2"))
+    return run_design_beside_qwen2(args, "damolorn", "Damolorn", args.damolorn_size, dam, qwen, z, runs)
+
+
+# ---------------------------------------------------------------------------------------
+# --workload dedizen: the design with chunked sink attention beside linear attention, an mLSTM
+# and RG-LRU layers, beside the dense Qwen2 shape of equal width, equal number of layers and a
+# feed-forward of equal weight count.
+
+DEDIZEN_SIZES = {
+    # width; attention heads / key heads / head size / chunk; memory heads x dim x vdim; mLSTM heads x dim x vdim;
+    # RG-LRU channels / blocks; ungated feed-forward; the gated feed-forward of equal weight count
+    "2k": dict(width=2048, heads=16, kv_heads=4, dim=128, chunk=1024, mem=(16, 64, 128), mlstm=(8, 128, 256),
+               lru=2560, lru_blocks=10, ff=8192, qwen_ff=5504),
+    "4k": dict(width=4096, heads=32, kv_heads=8, dim=128, chunk=2048, mem=(32, 64, 128), mlstm=(8, 256, 512),
+               lru=5120, lru_blocks=20, ff=16384, qwen_ff=10880),
+}
+
+
+def dedizen_config(size: str, vocab: int = 32000) -> dict:
+    """Six layers: parallel, mLSTM, RG-LRU, RG-LRU, parallel, mLSTM, each with a feed-forward."""
+    z = DEDIZEN_SIZES[size]
+    mlp = {"kind": "dense", "ff": z["ff"]}
+    mh, md, mv = z["mem"]
+    parallel = {"type": "parallel", "mlp": mlp, "mixer": {
+        "left": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
+                 "mask": {"size": z["chunk"]}, "scale": z["dim"] ** -0.5,
+                 "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0,
+                                                                    "slow": 1.0}}},
+        "right": {"heads": mh, "dim": md, "vdim": mv, "decay": [1.0 - 2.0 ** (-5 - 3 * h / mh) for h in range(mh)]}}}
+    xh, xd, xv = z["mlstm"]
+    mlstm = {"type": "mlstm", "mlp": mlp, "mixer": {"heads": xh, "dim": xd, "vdim": xv, "gate_cap": 15.0}}
+    rglru = {"type": "rglru", "mlp": mlp, "mixer": {"width": z["lru"], "blocks": z["lru_blocks"], "conv": 4}}
+    return {"architecture": "Dedizen", "vocab": vocab, "width": z["width"], "norm": {"eps": 1e-5},
+            "layers": [parallel, mlstm, rglru, rglru, parallel, mlstm], "max_positions": 8192}
+
+
+def run_dedizen(args) -> dict:
+    from emberserve_b200.config.dedizen import DedizenConfig
+    from emberserve_b200.config.model import Qwen2Config
+
+    z = DEDIZEN_SIZES[args.dedizen_size]
+    ded = DedizenConfig.from_dict(dedizen_config(args.dedizen_size))
+    runs = len(ded.layers)
+    qwen = Qwen2Config.from_dict(dict(
+        SHAPE_7B, vocab_size=32000, hidden_size=z["width"], num_attention_heads=z["heads"],
+        num_key_value_heads=z["kv_heads"], head_dim=128, intermediate_size=z["qwen_ff"],
+        num_hidden_layers=runs, max_position_embeddings=8192, architectures=["Qwen2ForCausalLM"], model_type="qwen2"))
+    return run_design_beside_qwen2(args, "dedizen", "Dedizen", args.dedizen_size, ded, qwen,
+                                   {k: (list(v) if isinstance(v, tuple) else v) for k, v in z.items()}, runs)
+
+
+def run_design_beside_qwen2(args, key: str, label: str, size: str, dam, qwen, z: dict, runs: int) -> dict:
+    """Prompt and decode steps of one design and of the dense Qwen2 shape beside it, with device time per kernel."""
+    import torch
+
+    from emberserve_b200 import kernels as K
+    from emberserve_b200.engine.runner import ModelRunner, StepRow
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA GPU"
+    peaks = measured_peaks()
+    K.library()
     ctx_len, batches, prompts = args.decode_context if args.decode_context != CONTEXT else 2048, (8, 64), (512, 2048)
     dtype = torch.float32 if args.dtype == "float32" else torch.bfloat16
     gen = torch.Generator().manual_seed(1)
@@ -1038,12 +1092,11 @@ def run_damolorn(args) -> dict:
         return out
 
     if args.only in ("prefill", "decode"):
-        return {"workload": "damolorn", "size": args.damolorn_size, "only": args.only,
-                "damolorn": measure(dam, "Damolorn")}
-    ours = measure(dam, "Damolorn")
+        return {"workload": key, "size": size, "only": args.only, key: measure(dam, label)}
+    ours = measure(dam, label)
     beside = measure(qwen, "Qwen2 dense")
-    return {"workload": "damolorn", "size": args.damolorn_size, "dtype": args.dtype, "layer_runs": runs,
-            "context": ctx_len, "shape": z, "peaks": peaks, "damolorn": ours, "qwen2": beside,
+    return {"workload": key, "size": size, "dtype": args.dtype, "layer_runs": runs,
+            "context": ctx_len, "shape": z, "peaks": peaks, key: ours, "qwen2": beside,
             "data": "synthetic: uniform random token ids, random weights N(0,0.02) seed 0"}
 
 
@@ -1054,14 +1107,16 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--workload", choices=["decode-7b", "serve-0.5b", "mixed-32b", "fp32-7b", "damolorn"],
+    ap.add_argument("--workload", choices=["decode-7b", "serve-0.5b", "mixed-32b", "fp32-7b", "damolorn", "dedizen"],
                     default="decode-7b",
                     help="decode-7b: the headline line; serve-0.5b: continuous batching of --requests requests; "
                          "mixed-32b: chunked prefill of long prompts beside decode at the 32B shape; fp32-7b: "
                          "the true 32-bit path (the headline line runs the last three as child processes); "
                          "damolorn: prompt and decode steps of the Damolorn design at --damolorn-size beside the "
-                         "dense Qwen2 shape of equal width, layer runs and active feed-forward width")
+                         "dense Qwen2 shape of equal width, layer runs and active feed-forward width; dedizen: the "
+                         "same for the Dedizen design at --dedizen-size (equal width, layers and feed-forward weights)")
     ap.add_argument("--damolorn-size", choices=sorted(DAMOLORN_SIZES), default="2k")
+    ap.add_argument("--dedizen-size", choices=sorted(DEDIZEN_SIZES), default="2k")
     ap.add_argument("--no-extras", action="store_true",
                     help="the headline line without the points that need other models or kernels alone")
     ap.add_argument("--requests", type=int, default=256)
@@ -1117,6 +1172,9 @@ def main() -> int:
         args.warmup = 3
     if args.workload == "damolorn":
         print(json.dumps(run_damolorn(args)))
+        return 0
+    if args.workload == "dedizen":
+        print(json.dumps(run_dedizen(args)))
         return 0
     if args.only == "kernel":
         print(json.dumps(run_kernel(args)))

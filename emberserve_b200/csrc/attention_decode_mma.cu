@@ -83,7 +83,8 @@ decode_attention_mma_kernel(const DecodeParams p) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tok = p.cu_q[b];
     const int ctx = p.starts[b] + 1;           // keys visible to the query: [k_begin, ctx)
-    const int k_begin = p.window > 0 ? max(0, ctx - p.window) : 0;
+    const int k_begin = first_visible(ctx - 1, p.window, p.chunk);
+    const bool ext = p.chunk > 0 || p.sinks != nullptr || p.gate != nullptr;  // then the weights keep 16 bits (see below)
     const int G = p.G;
 
     // this block's tiles (16 keys each, aligned to absolute positions), and this warp's
@@ -302,6 +303,13 @@ decode_attention_mma_kernel(const DecodeParams p) {
         pa[1] = pack_bf16(s[0][2], s[0][3]);
         pa[2] = pack_bf16(s[1][0], s[1][1]);
         pa[3] = pack_bf16(s[1][2], s[1][3]);
+        uint32_t pr[4] = {0u, 0u, 0u, 0u};
+        if (ext) {
+            pr[0] = pack_bf16(s[0][0] - __uint_as_float(pa[0] << 16), s[0][1] - __uint_as_float(pa[0] & 0xffff0000u));
+            pr[1] = pack_bf16(s[0][2] - __uint_as_float(pa[1] << 16), s[0][3] - __uint_as_float(pa[1] & 0xffff0000u));
+            pr[2] = pack_bf16(s[1][0] - __uint_as_float(pa[2] << 16), s[1][1] - __uint_as_float(pa[2] & 0xffff0000u));
+            pr[3] = pack_bf16(s[1][2] - __uint_as_float(pa[3] << 16), s[1][3] - __uint_as_float(pa[3] & 0xffff0000u));
+        }
         {
             const int mat = lane >> 3, r = lane & 7;
             const int vrow = (mat & 1) * 8 + r;
@@ -312,6 +320,10 @@ decode_attention_mma_kernel(const DecodeParams p) {
                 ldmatrix_x4_trans(vst + vrow * ROW_BYTES + ((chunk ^ (vrow & 7)) << 4), bfrag);
                 mma_bf16_16816(o[2 * np], pa, bfrag[0], bfrag[1]);
                 mma_bf16_16816(o[2 * np + 1], pa, bfrag[2], bfrag[3]);
+                if (ext) {  // what the rounding of the weights to bfloat16 left over, as a second term
+                    mma_bf16_16816(o[2 * np], pr, bfrag[0], bfrag[1]);
+                    mma_bf16_16816(o[2 * np + 1], pr, bfrag[2], bfrag[3]);
+                }
             }
         }
         __syncwarp();  // every lane is done with the stage before it is refilled
@@ -359,7 +371,10 @@ decode_attention_mma_kernel(const DecodeParams p) {
         }
         const size_t prow = (size_t)tok * p.nh + (size_t)hk * G + g;
         if (p.splits == 1) {
-            p.out[prow * D + d] = __float2bfloat16_rn(acc / L);
+            if (p.sinks) L += exp2f(p.sinks[hk * G + g] * 1.4426950408889634f - M);
+            float y = acc / L;
+            if (p.gate) y *= 1.f / (1.f + expf(-__bfloat162float(p.gate[(size_t)tok * p.gate_stride + hk * G + g])));
+            p.out[prow * D + d] = __float2bfloat16_rn(y);
         } else {
             p.part_o[(prow * p.splits + split) * D + d] = acc;
             if (d == 0) {

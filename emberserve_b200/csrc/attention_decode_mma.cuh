@@ -26,7 +26,19 @@ struct DecodeParams {
     int rot = 0;        // 0 (no rotation) or D
     int fused = 0;
     int write_kv = 0;
+    // Beyond the plain causal form, in the kernels that say they take it (all optional):
+    int chunk = 0;                  // > 0: the query at p sees only keys j with j / chunk == p / chunk
+    const float* sinks = nullptr;   // [nh]: exp(sinks[h]) joins the softmax's denominator
+    const bf16* gate = nullptr;     // [N, gate_stride]: head h's output times sigmoid(gate[n, h])
+    long long gate_stride = 0;
 };
+
+// The first key that the query at position p may see.
+__host__ __device__ __forceinline__ int first_visible(int p, int window, int chunk) {
+    int lo = window > 0 ? (p - window + 1 > 0 ? p - window + 1 : 0) : 0;
+    if (chunk > 0 && (p / chunk) * chunk > lo) lo = (p / chunk) * chunk;
+    return lo;
+}
 
 bool decode_mma_supported(int dtype, int D, int G, long long q_stride, const void* q, const void* kc,
                           const void* vc);
@@ -39,6 +51,10 @@ bool decode_fused_supported(int D, int G, int rot, long long q_stride, const voi
 bool prefill_mma_supported(int dtype, int D, long long q_stride, const void* q, const void* out,
                            const void* kc, const void* vc);
 int run_prefill_mma(const DecodeParams& p, int B, int D, int max_q_len, cudaStream_t stream);
+// The same kernel with a chunk mask, sinks and a gate per head (DecodeParams::chunk, sinks, gate); the
+// softmax weights enter the second product as two bfloat16 terms (value and remainder), so that they
+// carry 16 bits of mantissa instead of 8.
+int run_prefill_mma_masked(const DecodeParams& p, int B, int D, int max_q_len, cudaStream_t stream);
 
 // The tcgen05 kernel for prompt portions (attention_prefill_tc05.cu): long prompts at head
 // sizes 64 and 128 with pages of a multiple of 16 keys; same parameter block.

@@ -44,13 +44,6 @@ struct AttnParams {
     long long gate_stride = 0;
 };
 
-// The first key that the query at position p may see.
-__device__ __forceinline__ int first_visible(int p, int window, int chunk) {
-    int lo = window > 0 ? max(0, p - window + 1) : 0;
-    if (chunk > 0) lo = max(lo, (p / chunk) * chunk);
-    return lo;
-}
-
 template <typename T, int VEC> struct VecLoad;
 template <> struct VecLoad<float, 4> {
     static __device__ __forceinline__ void load(const float* p, float* dst) {
@@ -351,7 +344,6 @@ static int paged_attention_any(const void* q, long long q_stride, void* out, int
     // the tensor-core kernels know the plain causal form (and a window)
     const bool plain = chunk <= 0 && !sinks && !gate;
     if (!plain && impl == 2) return EMS_ERR_SHAPE;
-    if (!plain) impl = 1;
     if ((q_stride * esize) % 16 || ((uintptr_t)q % 16) || ((uintptr_t)kcache % 16) || ((uintptr_t)vcache % 16))
         return EMS_ERR_ALIGN;
     AttnParams p;
@@ -373,6 +365,25 @@ static int paged_attention_any(const void* q, long long q_stride, void* out, int
     d.q_stride = q_stride; d.bt_stride = bt_stride; d.page_size = page_size; d.nh = nh; d.nkv = nkv;
     d.G = p.G; d.window = window; d.splits = splits;
     d.scale_log2 = scale * 1.4426950408889634f;
+    d.chunk = chunk; d.sinks = sinks; d.gate = reinterpret_cast<const bf16*>(gate); d.gate_stride = gate_stride;
+    if (!plain) {
+        // prompt portions on the tensor cores where the sizes allow; everything else on the generic kernel
+        if ((impl == 0 || impl == 3) && splits == 1 && max_q_len > 1 &&
+            prefill_mma_supported(dtype, D, q_stride, q, out, kcache, vcache) && (gate_stride * 2) % 2 == 0)
+            return run_prefill_mma_masked(d, B, D, max_q_len, stream);
+        if ((impl == 0 || impl == 3) && max_q_len == 1 && N == B &&
+            decode_mma_supported(dtype, D, p.G, q_stride, q, kcache, vcache)) {
+            const int rc = run_decode_mma(d, B, D, stream);
+            if (rc != EMS_OK || splits == 1) return rc;
+            return launch_pdl(attention_merge_kernel<bf16>, dim3((unsigned)((size_t)N * nh)),
+                              dim3(D >= 128 ? 128 : 64), 0, stream, (const float*)p.part_o, (const float*)p.part_ml,
+                              reinterpret_cast<bf16*>(out), splits, D, sinks, nh, reinterpret_cast<const bf16*>(gate),
+                              gate_stride);
+        }
+        if (dtype == EMS_F32) return run_attention<float>(p, B, N, max_q_len, stream);
+        if (dtype == EMS_BF16) return run_attention<bf16>(p, B, N, max_q_len, stream);
+        return EMS_ERR_DTYPE;
+    }
     // impl 2 asks for the tcgen05 prompt kernel whatever the length (tests); by default it takes
     // the portions whose longest request fills eight of its 256-row blocks per KV head, below
     // which the mma.sync kernel with its smaller tiles was measured to be as fast or faster.

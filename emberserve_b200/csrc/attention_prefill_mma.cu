@@ -54,7 +54,22 @@ __device__ __forceinline__ uint32_t pf_pack(float lo, float hi) {
 
 // PAGE16: the page size is a multiple of 16, so every aligned group of 16 keys of a tile
 // lies in one page, contiguously: a warp fetches one such group with one block-table lookup.
-template <int D, bool PAGE16>
+// the two halves of a packed pair of bfloat16, widened
+__device__ __forceinline__ float pf_lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float pf_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+
+// 1 / (sum of a row's softmax terms), with the row's sink in the sum and its gate on the result.
+// `m` is the row's maximum in the base-2 units of the loop (score * scale * log2 e).
+__device__ __forceinline__ float pf_finish(const DecodeParams& p, float l, float m, int token, int head) {
+    if (p.sinks) l += exp2f(p.sinks[head] * 1.4426950408889634f - m);
+    float inv = 1.0f / l;
+    if (p.gate) inv *= 1.f / (1.f + expf(-__bfloat162float(p.gate[(size_t)token * p.gate_stride + head])));
+    return inv;
+}
+
+// EXT: the kernel also honours DecodeParams::chunk, sinks and gate, and feeds the softmax weights to
+// the second product as value + remainder (two bfloat16 terms).
+template <int D, bool PAGE16, bool EXT = false>
 __global__ void __launch_bounds__(PF_WARPS * 32)
 prefill_attention_mma_kernel(const DecodeParams p) {
     constexpr int CH = D / 8;                 // 16-byte chunks per row
@@ -78,7 +93,8 @@ prefill_attention_mma_kernel(const DecodeParams p) {
 
     const int tok_lo = r0 / G, tok_hi = min(nrows - 1, r0 + PF_BQ - 1) / G;
     const int p_lo = start + tok_lo, p_hi = start + tok_hi;
-    const int k_begin = p.window > 0 ? max(0, p_lo - p.window + 1) : 0;
+    const int chunk = EXT ? p.chunk : 0;
+    const int k_begin = first_visible(p_lo, p.window, chunk);
     const int k_end = p_hi + 1;
     const int kt0 = (k_begin / PF_BK) * PF_BK;
     const int ntiles = (k_end - kt0 + PF_BK - 1) / PF_BK;
@@ -146,6 +162,11 @@ prefill_attention_mma_kernel(const DecodeParams p) {
     const int wr_lo = r0 + warp * 16, wr_hi = min(nrows - 1, wr_lo + 15);
     const int wpos_lo = wr_lo < nrows ? start + wr_lo / G : -1;
     const int wpos_hi = wr_lo < nrows ? start + wr_hi / G : -1;
+    // first visible key of this thread's rows and of the warp's first and last row (it grows with the position)
+    const int qlo0 = qpos0 >= 0 ? first_visible(qpos0, p.window, chunk) : 0;
+    const int qlo1 = qpos1 >= 0 ? first_visible(qpos1, p.window, chunk) : 0;
+    const int wlo_min = wpos_lo >= 0 ? first_visible(wpos_lo, p.window, chunk) : 0;
+    const int wlo_max = wpos_hi >= 0 ? first_visible(wpos_hi, p.window, chunk) : 0;
 
     uint32_t qf[KS][4];
     float o[D / 8][4];
@@ -168,7 +189,7 @@ prefill_attention_mma_kernel(const DecodeParams p) {
             }
         }
         const int kt = kt0 + t * PF_BK;
-        const bool warp_sees = wpos_hi >= kt && (p.window <= 0 || kt + PF_BK - 1 > wpos_lo - p.window);
+        const bool warp_sees = wpos_hi >= kt && kt + PF_BK - 1 >= wlo_min;
         if (warp_sees) {
             const uint32_t kst = kv_s + (t & 1) * 2 * KV_BYTES, vst = kst + KV_BYTES;
             float s[PF_BK / 8][4];
@@ -191,15 +212,15 @@ prefill_attention_mma_kernel(const DecodeParams p) {
             }
             // mask (only tiles that touch the diagonal or the window's edge need one), online
             // softmax in base 2: p = 2^(s * scale_log2 - m), one FMA and one ex2 per score
-            const bool full = kt + PF_BK - 1 <= wpos_lo && (p.window <= 0 || kt > wpos_hi - p.window);
+            const bool full = kt + PF_BK - 1 <= wpos_lo && kt >= wlo_max;
             if (!full) {
 #pragma unroll
                 for (int n = 0; n < PF_BK / 8; ++n)
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const int key = kt + n * 8 + (lane & 3) * 2 + e;
-                        const bool v0 = key <= qpos0 && (p.window <= 0 || key > qpos0 - p.window);
-                        const bool v1 = key <= qpos1 && (p.window <= 0 || key > qpos1 - p.window);
+                        const bool v0 = key <= qpos0 && key >= qlo0;
+                        const bool v1 = key <= qpos1 && key >= qlo1;
                         if (!v0) s[n][e] = -INFINITY;
                         if (!v1) s[n][2 + e] = -INFINITY;
                     }
@@ -243,14 +264,25 @@ prefill_attention_mma_kernel(const DecodeParams p) {
                     pa[1] = pf_pack(s[2 * kc][2], s[2 * kc][3]);
                     pa[2] = pf_pack(s[2 * kc + 1][0], s[2 * kc + 1][1]);
                     pa[3] = pf_pack(s[2 * kc + 1][2], s[2 * kc + 1][3]);
+                    uint32_t pr[4];  // what the rounding of the weights to bfloat16 left over (EXT)
+                    if (EXT) {
+                        pr[0] = pf_pack(s[2 * kc][0] - pf_lo(pa[0]), s[2 * kc][1] - pf_hi(pa[0]));
+                        pr[1] = pf_pack(s[2 * kc][2] - pf_lo(pa[1]), s[2 * kc][3] - pf_hi(pa[1]));
+                        pr[2] = pf_pack(s[2 * kc + 1][0] - pf_lo(pa[2]), s[2 * kc + 1][1] - pf_hi(pa[2]));
+                        pr[3] = pf_pack(s[2 * kc + 1][2] - pf_lo(pa[3]), s[2 * kc + 1][3] - pf_hi(pa[3]));
+                    }
                     const int vrow = kc * 16 + (mat & 1) * 8 + r;
 #pragma unroll
                     for (int np = 0; np < KS; ++np) {
-                        const int chunk = np * 2 + (mat >> 1);
+                        const int vchunk = np * 2 + (mat >> 1);
                         uint32_t bfrag[4];
-                        pf_ldsm4t(vst + vrow * ROW_BYTES + ((chunk ^ (vrow & 7)) << 4), bfrag);
+                        pf_ldsm4t(vst + vrow * ROW_BYTES + ((vchunk ^ (vrow & 7)) << 4), bfrag);
                         pf_mma(o[2 * np], pa, bfrag[0], bfrag[1]);
                         pf_mma(o[2 * np + 1], pa, bfrag[2], bfrag[3]);
+                        if (EXT) {
+                            pf_mma(o[2 * np], pr, bfrag[0], bfrag[1]);
+                            pf_mma(o[2 * np + 1], pr, bfrag[2], bfrag[3]);
+                        }
                     }
                 }
             }
@@ -266,24 +298,26 @@ prefill_attention_mma_kernel(const DecodeParams p) {
     const int c = (lane & 3) * 2;
     if (gr0 < nrows) {
         bf16* dst = p.out + ((size_t)(q0 + gr0 / G) * p.nh + hk * G + gr0 % G) * D;
-        const float inv = 1.0f / l0;
+        float inv = 1.0f / l0;
+        if (EXT) inv = pf_finish(p, l0, m0, q0 + gr0 / G, hk * G + gr0 % G);
 #pragma unroll
         for (int n = 0; n < D / 8; ++n)
             *reinterpret_cast<__nv_bfloat162*>(dst + n * 8 + c) = __floats2bfloat162_rn(o[n][0] * inv, o[n][1] * inv);
     }
     if (gr1 < nrows) {
         bf16* dst = p.out + ((size_t)(q0 + gr1 / G) * p.nh + hk * G + gr1 % G) * D;
-        const float inv = 1.0f / l1;
+        float inv = 1.0f / l1;
+        if (EXT) inv = pf_finish(p, l1, m1, q0 + gr1 / G, hk * G + gr1 % G);
 #pragma unroll
         for (int n = 0; n < D / 8; ++n)
             *reinterpret_cast<__nv_bfloat162*>(dst + n * 8 + c) = __floats2bfloat162_rn(o[n][2] * inv, o[n][3] * inv);
     }
 }
 
-template <int D, bool PAGE16>
+template <int D, bool PAGE16, bool EXT = false>
 int launch_prefill_mma(const DecodeParams& p, int B, int max_q_len, cudaStream_t stream) {
     constexpr int smem = PF_BQ * D * 2 + 2 * 2 * PF_BK * D * 2;
-    auto kernel = prefill_attention_mma_kernel<D, PAGE16>;
+    auto kernel = prefill_attention_mma_kernel<D, PAGE16, EXT>;
     if (smem > 48 * 1024 &&
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
         return EMS_ERR_LAUNCH;
@@ -309,6 +343,14 @@ int run_prefill_mma(const DecodeParams& p, int B, int D, int max_q_len, cudaStre
                        : launch_prefill_mma<128, true>(p, B, max_q_len, stream);
     return D == 64 ? launch_prefill_mma<64, false>(p, B, max_q_len, stream)
                    : launch_prefill_mma<128, false>(p, B, max_q_len, stream);
+}
+
+int run_prefill_mma_masked(const DecodeParams& p, int B, int D, int max_q_len, cudaStream_t stream) {
+    if (p.page_size % 16 == 0)
+        return D == 64 ? launch_prefill_mma<64, true, true>(p, B, max_q_len, stream)
+                       : launch_prefill_mma<128, true, true>(p, B, max_q_len, stream);
+    return D == 64 ? launch_prefill_mma<64, false, true>(p, B, max_q_len, stream)
+                   : launch_prefill_mma<128, false, true>(p, B, max_q_len, stream);
 }
 
 }  // namespace ems

@@ -34,10 +34,18 @@ __device__ __forceinline__ float in_act(float z, int act) { return act == EMS_IN
 
 // ---------------------------------------------------------------------------------------
 // matrix memory
+//
+// A block of 16 warps owns a group of columns of one head's [v | 1] (the column of ones carries the
+// normaliser) for one request.  A column is shared by SL lanes (32, 16 or 8, by the head's rows D);
+// lane s holds rows i * 4 SL + 4 s + e (e < 4, i < DPT / 4) of the column of S in registers, so that
+// the lanes of a warp read a staged q or k row as consecutive float4 and the dot product with q
+// closes with log2(SL) shuffles.  The step's tokens are staged in tiles: q (scaled) and k (times
+// b_t) widened and passed through the activation once; rows past D are zero.  A tile's inputs are
+// asked for, as they lie in memory, while the tile before is computed, and widened when staged.
+// Per token a thread does DPT multiply-adds into S and DPT into the read; only S carries from token
+// to token, and with four warps per scheduler the latencies of one warp hide behind the others.
 
-constexpr int MR_TT = 16;     // tokens staged per tile
-constexpr int MR_COLS = 64;   // value columns per block (8 warps x 8 columns)
-constexpr int MR_SLICES = 4;  // lanes that share a column: each holds every fourth row of S
+constexpr int MR_WARPS = 16;
 
 struct MatRecParams {
     const void* q; const void* k; const void* v;   // [N, ld*] views; head h begins at column h * D (h * V)
@@ -51,25 +59,49 @@ struct MatRecParams {
     const int* slots;           // [rows]
     const int* cu_q;            // [rows + 1]
     float* out;                 // [N, H * V] float
-    int H, D, V, head_stride, normaliser, act;
+    int H, D, V, head_stride, normaliser, act, vec_ok;
     float q_scale, denom_eps;
 };
 
-template <typename T, int DPT>
-__global__ void __launch_bounds__(256) matrix_recurrence_kernel(const MatRecParams p) {
-    extern __shared__ float smem[];
+// four consecutive elements of a row as they lie in memory (one 8- or 16-byte load), widened later:
+// a tile's loads are all issued before any of them is looked at
+template <typename T> struct Raw4;
+template <> struct Raw4<float> {
+    typedef float4 type;
+    static __device__ __forceinline__ float4 widen(const float4& r) { return r; }
+};
+template <> struct Raw4<bf16> {
+    typedef uint2 type;
+    static __device__ __forceinline__ float4 widen(const uint2& r) {
+        const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x));
+        const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
+        return make_float4(lo.x, lo.y, hi.x, hi.y);
+    }
+};
+
+template <typename T, int DPT, int SL, int TT, bool VEC>
+__global__ void __launch_bounds__(MR_WARPS * 32) matrix_recurrence_kernel(const MatRecParams p) {
+    constexpr int THREADS = MR_WARPS * 32;
+    constexpr int DP = SL * DPT;                   // rows the block can hold (>= D)
+    constexpr int WCOLS = 32 / SL;                 // columns per warp
+    constexpr int COLS = MR_WARPS * WCOLS;         // columns per block
+    constexpr int GROUPS = TT * (DP / 4);          // groups of four q / k rows per tile
+    constexpr int GPT = (GROUPS + THREADS - 1) / THREADS;
+    constexpr int VPT = (TT * COLS + THREADS - 1) / THREADS;
+    extern __shared__ __align__(16) float smem[];
     const int D = p.D, V = p.V;
-    float* qs = smem;                    // [TT][D]
-    float* ks = qs + MR_TT * D;          // [TT][D]   (already times b_t)
-    float* vs = ks + MR_TT * D;          // [TT][MR_COLS]
-    float* as = vs + MR_TT * MR_COLS;    // [TT]
+    float* qs = smem;                    // [TT][DP]
+    float* ks = qs + TT * DP;            // [TT][DP]   (already times b_t)
+    float* vs = ks + TT * DP;            // [TT][COLS]
+    float* as = vs + TT * COLS;          // [TT] decay
+    float* fs = as + TT;                 // [TT] floor of the denominator
     const int row = blockIdx.z, head = blockIdx.y;
     const int q0 = p.cu_q[row], qlen = p.cu_q[row + 1] - q0;
     if (qlen <= 0) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int slice = lane & (MR_SLICES - 1), colw = lane >> 2;
-    const int lcol = warp * 8 + colw;                  // column inside the block
-    const int col = blockIdx.x * MR_COLS + lcol;       // column of [v | 1]
+    const int slice = lane & (SL - 1), colw = lane / SL;
+    const int lcol = warp * WCOLS + colw;          // column inside the block
+    const int col = blockIdx.x * COLS + lcol;      // column of [v | 1]
     const int ncols = V + (p.normaliser ? 1 : 0);
     const bool live = col < ncols;
     const bool is_norm = p.normaliser && col == V;
@@ -78,67 +110,134 @@ __global__ void __launch_bounds__(256) matrix_recurrence_kernel(const MatRecPara
     float S[DPT];
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
-        const int d = i * MR_SLICES + slice;
+        const int d = (i / 4) * (4 * SL) + 4 * slice + (i & 3);
         S[i] = (live && d < D) ? (is_norm ? st[(size_t)D * V + d] : st[(size_t)d * V + col]) : 0.f;
     }
-    const T* qg = reinterpret_cast<const T*>(p.q);
-    const T* kg = reinterpret_cast<const T*>(p.k);
-    const T* vg = reinterpret_cast<const T*>(p.v);
+    const T* qg = reinterpret_cast<const T*>(p.q) + (size_t)head * D;
+    const T* kg = reinterpret_cast<const T*>(p.k) + (size_t)head * D;
+    const T* vg = reinterpret_cast<const T*>(p.v) + (size_t)head * V;
     const float decay_const = p.decay_head ? p.decay_head[head] : 1.f;
 
-    for (int t0 = 0; t0 < qlen; t0 += MR_TT) {
-        const int cnt = min(MR_TT, qlen - t0);
-        __syncthreads();  // the tile before is consumed
-        for (int idx = threadIdx.x; idx < cnt * D; idx += blockDim.x) {
-            const int t = idx / D, d = idx % D;
-            const size_t tok = (size_t)(q0 + t0 + t);
-            const float bt = p.b ? p.b[tok * p.H + head] : 1.f;
-            qs[t * D + d] = in_act(to_f32<T>(qg[tok * p.ldq + (size_t)head * D + d]), p.act) * p.q_scale;
-            ks[t * D + d] = in_act(to_f32<T>(kg[tok * p.ldk + (size_t)head * D + d]), p.act) * bt;
-        }
-        for (int idx = threadIdx.x; idx < cnt * MR_COLS; idx += blockDim.x) {
-            const int t = idx / MR_COLS, c = idx % MR_COLS;
-            const int gc = blockIdx.x * MR_COLS + c;
-            const size_t tok = (size_t)(q0 + t0 + t);
-            float val = 0.f;
-            if (gc < V) val = in_act(to_f32<T>(vg[tok * p.ldv + (size_t)head * V + gc]), p.act);
-            else if (p.normaliser && gc == V) val = 1.f;
-            vs[t * MR_COLS + c] = val;
-        }
-        if (threadIdx.x < cnt) {
-            const size_t tok = (size_t)(q0 + t0 + threadIdx.x);
-            as[threadIdx.x] = p.decay_head ? decay_const : p.a[tok * p.H + head];
-        }
-        __syncthreads();
-        for (int t = 0; t < cnt; ++t) {
-            const float a = as[t];
-            const float vj = vs[t * MR_COLS + lcol];
-            const float* kr = ks + t * D;
-            const float* qr = qs + t * D;
-            float acc = 0.f;
+    typedef typename Raw4<T>::type raw4;
+    float4 rq[VEC ? 1 : GPT], rk[VEC ? 1 : GPT];   // the scalar path (heads that do not begin aligned) widens at once
+    raw4 wq[VEC ? GPT : 1], wk[VEC ? GPT : 1];     // the aligned path keeps what it loaded and widens when it is staged
+    float rb[GPT], ra = 1.f, rf = 0.f;
+    T rv[VPT];
+    auto ask = [&](int t0) {
+        const int cnt = min(TT, qlen - t0);
 #pragma unroll
-            for (int i = 0; i < DPT; ++i) {
-                const int d = i * MR_SLICES + slice;
-                if (d < D) {
-                    S[i] = fmaf(a, S[i], kr[d] * vj);
-                    acc = fmaf(S[i], qr[d], acc);
+        for (int g = 0; g < GPT; ++g) {
+            const int idx = threadIdx.x + g * THREADS;
+            const int t = idx / (DP / 4), d = (idx % (DP / 4)) * 4;
+            const bool ok = idx < GROUPS && t < cnt && d < D;
+            const size_t tok = (size_t)(q0 + (ok ? t0 + t : 0));
+            if constexpr (VEC) {   // straight-line: every load is issued, groups out of range read the first row again
+                const int dd = ok ? d : 0;
+                wq[g] = *reinterpret_cast<const raw4*>(qg + tok * p.ldq + dd);
+                wk[g] = *reinterpret_cast<const raw4*>(kg + tok * p.ldk + dd);
+            } else {
+                rq[g] = make_float4(0.f, 0.f, 0.f, 0.f);
+                rk[g] = rq[g];
+                if (ok) {
+                    const T* qr = qg + tok * p.ldq + d;
+                    const T* kr = kg + tok * p.ldk + d;
+                    rq[g].x = to_f32<T>(qr[0]);
+                    rk[g].x = to_f32<T>(kr[0]);
+                    if (d + 1 < D) { rq[g].y = to_f32<T>(qr[1]); rk[g].y = to_f32<T>(kr[1]); }
+                    if (d + 2 < D) { rq[g].z = to_f32<T>(qr[2]); rk[g].z = to_f32<T>(kr[2]); }
+                    if (d + 3 < D) { rq[g].w = to_f32<T>(qr[3]); rk[g].w = to_f32<T>(kr[3]); }
                 }
             }
-            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+            rb[g] = p.b ? p.b[tok * p.H + head] : 1.f;
+        }
+#pragma unroll
+        for (int g = 0; g < VPT; ++g) {
+            const int idx = threadIdx.x + g * THREADS;
+            const int t = idx / COLS, gc = blockIdx.x * COLS + idx % COLS;
+            const bool ok = idx < TT * COLS && t < cnt && gc < V;
+            rv[g] = vg[(size_t)(q0 + (ok ? t0 + t : 0)) * p.ldv + (ok ? gc : 0)];
+        }
+        {
+            const bool ok = (int)threadIdx.x < cnt;
+            const size_t at = (size_t)(q0 + (ok ? t0 + (int)threadIdx.x : 0)) * p.H + head;
+            ra = p.decay_head ? decay_const : p.a[at];
+            rf = p.normaliser ? p.denom_floor[at] : 0.f;
+        }
+    };
+    ask(0);
+    for (int t0 = 0; t0 < qlen; t0 += TT) {
+        const int cnt = min(TT, qlen - t0);
+        __syncthreads();  // the tile before is consumed
+#pragma unroll
+        for (int g = 0; g < GPT; ++g) {
+            const int idx = threadIdx.x + g * THREADS;
+            if (idx < GROUPS) {
+                const int t = idx / (DP / 4), d = (idx % (DP / 4)) * 4;
+                const bool ok = t < cnt && d < D;   // (rows past D and tokens past the end are staged as zeros)
+                const float qsc = ok ? p.q_scale : 0.f, bt = ok ? rb[g] : 0.f;
+                float4 fq, fk;
+                if constexpr (VEC) { fq = Raw4<T>::widen(wq[g]); fk = Raw4<T>::widen(wk[g]); }
+                else { fq = rq[g]; fk = rk[g]; }
+                const float4 qq = make_float4(in_act(fq.x, p.act) * qsc, in_act(fq.y, p.act) * qsc,
+                                              in_act(fq.z, p.act) * qsc, in_act(fq.w, p.act) * qsc);
+                const float4 kk = make_float4(in_act(fk.x, p.act) * bt, in_act(fk.y, p.act) * bt,
+                                              in_act(fk.z, p.act) * bt, in_act(fk.w, p.act) * bt);
+                *reinterpret_cast<float4*>(qs + t * DP + d) = qq;
+                *reinterpret_cast<float4*>(ks + t * DP + d) = kk;
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < VPT; ++g) {
+            const int idx = threadIdx.x + g * THREADS;
+            if (idx < TT * COLS) {
+                const int gc = blockIdx.x * COLS + idx % COLS;
+                float val = 0.f;
+                if (idx / COLS < cnt) {
+                    if (gc < V) val = in_act(to_f32<T>(rv[g]), p.act);
+                    else if (p.normaliser && gc == V) val = 1.f;   // the column of ones
+                }
+                vs[idx] = val;
+            }
+        }
+        if ((int)threadIdx.x < TT) {
+            as[threadIdx.x] = ra;
+            fs[threadIdx.x] = rf;
+        }
+        __syncthreads();
+        if (t0 + TT < qlen) ask(t0 + TT);   // in flight while this tile is computed
+#pragma unroll 2
+        for (int t = 0; t < cnt; ++t) {
+            const float a = as[t];
+            const float vj = vs[t * COLS + lcol];
+            const float4* k4 = reinterpret_cast<const float4*>(ks + t * DP) + slice;
+            const float4* q4 = reinterpret_cast<const float4*>(qs + t * DP) + slice;
+            float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+#pragma unroll
+            for (int i = 0; i < DPT / 4; ++i) {
+                const float4 kk = k4[i * SL], qq = q4[i * SL];
+                S[4 * i + 0] = fmaf(a, S[4 * i + 0], kk.x * vj);
+                S[4 * i + 1] = fmaf(a, S[4 * i + 1], kk.y * vj);
+                S[4 * i + 2] = fmaf(a, S[4 * i + 2], kk.z * vj);
+                S[4 * i + 3] = fmaf(a, S[4 * i + 3], kk.w * vj);
+                acc0 = fmaf(S[4 * i + 0], qq.x, acc0);
+                acc1 = fmaf(S[4 * i + 1], qq.y, acc1);
+                acc2 = fmaf(S[4 * i + 2], qq.z, acc2);
+                acc3 = fmaf(S[4 * i + 3], qq.w, acc3);
+            }
+            float acc = (acc0 + acc1) + (acc2 + acc3);
+#pragma unroll
+            for (int off = 1; off < SL; off <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
             if (live && slice == 0) {
                 const size_t tok = (size_t)(q0 + t0 + t);
-                if (is_norm)
-                    p.denom[tok * p.H + head] = fmaxf(fabsf(acc), p.denom_floor[tok * p.H + head]) + p.denom_eps;
-                else
-                    p.out[tok * ((size_t)p.H * V) + (size_t)head * V + col] = acc;
+                if (is_norm) p.denom[tok * p.H + head] = fmaxf(fabsf(acc), fs[t]) + p.denom_eps;
+                else p.out[tok * ((size_t)p.H * V) + (size_t)head * V + col] = acc;
             }
         }
     }
     if (live) {
 #pragma unroll
         for (int i = 0; i < DPT; ++i) {
-            const int d = i * MR_SLICES + slice;
+            const int d = (i / 4) * (4 * SL) + 4 * slice + (i & 3);
             if (d < D) {
                 if (is_norm) st[(size_t)D * V + d] = S[i];
                 else st[(size_t)d * V + col] = S[i];
@@ -147,20 +246,78 @@ __global__ void __launch_bounds__(256) matrix_recurrence_kernel(const MatRecPara
     }
 }
 
+// A step in which every request brings one token: the state is read and written once and nothing
+// else matters.  A thread owns a column of [v | 1] and walks its rows, so that the lanes of a warp
+// touch consecutive floats of every row of S.
 template <typename T>
-static int launch_matrix_recurrence(const MatRecParams& p, int rows, cudaStream_t stream) {
+__global__ void __launch_bounds__(128) matrix_step_kernel(const MatRecParams p) {
+    __shared__ float qs[256], ks[256];
+    const int D = p.D, V = p.V;
+    const int tok = blockIdx.z, head = blockIdx.y;   // (row r brings token r)
+    const float bt = p.b ? p.b[(size_t)tok * p.H + head] : 1.f;
+    const T* qg = reinterpret_cast<const T*>(p.q) + (size_t)tok * p.ldq + (size_t)head * D;
+    const T* kg = reinterpret_cast<const T*>(p.k) + (size_t)tok * p.ldk + (size_t)head * D;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        qs[d] = in_act(to_f32<T>(qg[d]), p.act) * p.q_scale;
+        ks[d] = in_act(to_f32<T>(kg[d]), p.act) * bt;
+    }
+    __syncthreads();
+    const int col = blockIdx.x * blockDim.x + threadIdx.x;
+    const int ncols = V + (p.normaliser ? 1 : 0);
+    if (col >= ncols) return;
+    const bool is_norm = p.normaliser && col == V;
+    const float a = p.decay_head ? p.decay_head[head] : p.a[(size_t)tok * p.H + head];
+    const float vj = is_norm ? 1.f : in_act(to_f32<T>(reinterpret_cast<const T*>(p.v)[(size_t)tok * p.ldv + (size_t)head * V + col]), p.act);
+    float* st = p.state + ((size_t)p.slots[tok] * p.H + head) * p.head_stride;
+    float* sp = is_norm ? st + (size_t)D * V : st + col;
+    const size_t step = is_norm ? 1 : (size_t)V;
+    float acc0 = 0.f, acc1 = 0.f;
+    int d = 0;
+    for (; d + 1 < D; d += 2) {
+        const float s0 = fmaf(a, sp[d * step], ks[d] * vj), s1 = fmaf(a, sp[(d + 1) * step], ks[d + 1] * vj);
+        sp[d * step] = s0;
+        sp[(d + 1) * step] = s1;
+        acc0 = fmaf(s0, qs[d], acc0);
+        acc1 = fmaf(s1, qs[d + 1], acc1);
+    }
+    if (d < D) {
+        const float s0 = fmaf(a, sp[d * step], ks[d] * vj);
+        sp[d * step] = s0;
+        acc0 = fmaf(s0, qs[d], acc0);
+    }
+    const float acc = acc0 + acc1;
+    if (is_norm) p.denom[(size_t)tok * p.H + head] = fmaxf(fabsf(acc), p.denom_floor[(size_t)tok * p.H + head]) + p.denom_eps;
+    else p.out[(size_t)tok * ((size_t)p.H * V) + (size_t)head * V + col] = acc;
+}
+
+template <typename T, int DPT, int SL, int TT>
+static int launch_matrix_recurrence_as(const MatRecParams& p, int rows, cudaStream_t stream) {
+    constexpr int COLS = MR_WARPS * (32 / SL);
     const int ncols = p.V + (p.normaliser ? 1 : 0);
-    const dim3 grid((ncols + MR_COLS - 1) / MR_COLS, p.H, rows);
-    int threads = 32 * ((min(ncols, MR_COLS) + 7) / 8);
-    const size_t smem = sizeof(float) * ((size_t)MR_TT * (2 * p.D + MR_COLS) + MR_TT);
-    if (smem > 48 * 1024) return EMS_ERR_SHAPE;
-    const int need = (p.D + MR_SLICES - 1) / MR_SLICES;
-    if (need <= 8) matrix_recurrence_kernel<T, 8><<<grid, threads, smem, stream>>>(p);
-    else if (need <= 16) matrix_recurrence_kernel<T, 16><<<grid, threads, smem, stream>>>(p);
-    else if (need <= 32) matrix_recurrence_kernel<T, 32><<<grid, threads, smem, stream>>>(p);
-    else if (need <= 64) matrix_recurrence_kernel<T, 64><<<grid, threads, smem, stream>>>(p);
-    else return EMS_ERR_SHAPE;
+    const dim3 grid((ncols + COLS - 1) / COLS, p.H, rows);
+    const size_t smem = sizeof(float) * ((size_t)TT * (2 * SL * DPT + COLS) + 2 * TT);
+    if (p.vec_ok) matrix_recurrence_kernel<T, DPT, SL, TT, true><<<grid, MR_WARPS * 32, smem, stream>>>(p);
+    else matrix_recurrence_kernel<T, DPT, SL, TT, false><<<grid, MR_WARPS * 32, smem, stream>>>(p);
     return launch_status();
+}
+
+template <typename T>
+static int launch_matrix_recurrence(MatRecParams& p, int rows, int N, cudaStream_t stream) {
+    // 8- or 16-byte loads of four q / k elements where every row and head begins aligned
+    const int e = (int)sizeof(T);
+    p.vec_ok = p.D % 4 == 0 && p.ldq % 4 == 0 && p.ldk % 4 == 0 && ((uintptr_t)p.q % (4 * e)) == 0 &&
+               ((uintptr_t)p.k % (4 * e)) == 0;
+    if (p.D > 256) return EMS_ERR_SHAPE;
+    if (N == rows) {   // every request brings one token
+        const int ncols = p.V + (p.normaliser ? 1 : 0);
+        matrix_step_kernel<T><<<dim3((ncols + 127) / 128, p.H, rows), 128, 0, stream>>>(p);
+        return launch_status();
+    }
+    if (p.D <= 32) return launch_matrix_recurrence_as<T, 4, 8, 32>(p, rows, stream);
+    if (p.D <= 64) return launch_matrix_recurrence_as<T, 4, 16, 32>(p, rows, stream);
+    if (p.D <= 128) return launch_matrix_recurrence_as<T, 4, 32, 32>(p, rows, stream);
+    if (p.D <= 256) return launch_matrix_recurrence_as<T, 8, 32, 16>(p, rows, stream);
+    return EMS_ERR_SHAPE;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -244,43 +401,131 @@ __global__ void group_norm_gate_kernel(const float* __restrict__ o, const float*
 }
 
 // ---------------------------------------------------------------------------------------
-// the gated diagonal recurrence.  A thread owns (request, channel).  Gate pre-activations arrive
-// as [2, blocks, N, C / blocks] float (r then i; the layout that one batched product per gate over
-// the blocks of a block-diagonal matrix leaves): r = sigmoid(pre_r + br), i = sigmoid(pre_i + bi),
-// log a = -c r softplus(lam), S = a S + sqrt(1 - a^2) i u, out = S * gelu_tanh(y).
+// the gated diagonal recurrence.  Gate pre-activations arrive as [2, blocks, N, C / blocks] float (r
+// then i; the layout that one batched product per gate over the blocks of a block-diagonal matrix
+// leaves): r = sigmoid(pre_r + br), i = sigmoid(pre_i + bi), log a = -c r softplus(lam),
+// S = a S + sqrt(1 - a^2) i u, out = S * gelu_tanh(y).
+//
+// A block owns 32 channels of one request and walks its tokens in tiles of 32.  Per tile: with a
+// lane per channel the threads load the tile and compute (a, b, gate) of every (token, channel);
+// through shared memory the tile is turned so that a warp owns a channel with a lane per token and
+// the recurrence S_t = a_t S_(t-1) + b_t becomes a scan of affine maps over the lanes (five
+// shuffle steps), continued from the carry of the tile before; turned back, the threads store
+// S * gate with a lane per channel.  The next tile's loads are issued before the scan.
+
+constexpr int LRU_T = 32;   // tokens per tile
+constexpr int LRU_C = 16;   // channels per block
+constexpr int LRU_W = 8;    // warps
 
 template <typename T>
-__global__ void rglru_scan_kernel(const T* __restrict__ u, const float* __restrict__ pre,
-                                  const void* __restrict__ br, const void* __restrict__ bi,
-                                  const void* __restrict__ lam, int p_dtype, const T* __restrict__ y, long long ldy,
-                                  int y_act, float cmul, float* __restrict__ state, const int* __restrict__ slots,
-                                  const int* __restrict__ cu_q, T* __restrict__ out, int N, int C, int blocks) {
+__global__ void __launch_bounds__(LRU_W * 32)
+rglru_scan_kernel(const T* __restrict__ u, const float* __restrict__ pre, const void* __restrict__ br,
+                  const void* __restrict__ bi, const void* __restrict__ lam, int p_dtype, const T* __restrict__ y,
+                  long long ldy, int y_act, float cmul, float* __restrict__ state, const int* __restrict__ slots,
+                  const int* __restrict__ cu_q, T* __restrict__ out, int N, int C, int blocks) {
+    __shared__ float sa[LRU_T][LRU_C + 1], sb[LRU_T][LRU_C + 1], sg[LRU_T][LRU_C + 1], carry[LRU_C];
     const int row = blockIdx.y;
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= C) return;
     const int q0 = cu_q[row], qlen = cu_q[row + 1] - q0;
     if (qlen <= 0) return;
-    const int bw = C / blocks, blk = c / bw, j = c % bw;
-    const float rb = load_any(br, p_dtype, c), ib = load_any(bi, p_dtype, c);
-    const float sp = cmul * softplus_f(load_any(lam, p_dtype, c));
-    float* sp_state = state + (size_t)slots[row] * C + c;
-    float S = *sp_state;
-    const float* pr = pre + ((size_t)blk * N + q0) * bw + j;   // the r gate; the i gate lies N * C further
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // loading and storing: a thread owns a channel and every ROWS-th token of the tile
+    constexpr int ROWS = LRU_W * 32 / LRU_C, PER = LRU_T / ROWS;
+    const int lc = threadIdx.x % LRU_C, lt = threadIdx.x / LRU_C;
+    const int c = blockIdx.x * LRU_C + lc;
+    const bool has_c = c < C;
+    const int bw = C / blocks;
+    const int cc = has_c ? c : 0;
+    const float rb = load_any(br, p_dtype, cc), ib = load_any(bi, p_dtype, cc);
+    const float sp = cmul * softplus_f(load_any(lam, p_dtype, cc));
+    const float* pr = pre + ((size_t)(cc / bw) * N + q0) * bw + cc % bw;   // the r gate; the i gate lies N * C further
     const size_t gate_i = (size_t)N * C;
-#pragma unroll 4
-    for (int t = 0; t < qlen; ++t) {
-        const size_t tok = (size_t)(q0 + t);
-        const float r = sigmoid_f(pr[(size_t)t * bw] + rb);
-        const float ig = sigmoid_f(pr[(size_t)t * bw + gate_i] + ib);
-        const float log_a = -sp * r;
-        const float a = expf(log_a);
-        const float mult = sqrtf(-expm1f(2.f * log_a));   // sqrt(1 - a^2) without the cancellation
-        S = fmaf(a, S, mult * ig * to_f32<T>(u[tok * C + c]));
-        float yy = to_f32<T>(y[tok * ldy + c]);
-        if (y_act) yy = gelu_tanh_f(yy);
-        out[tok * C + c] = from_f32<T>(S * yy);
+    float* st = state + (size_t)slots[row] * C;
+    if (threadIdx.x < LRU_C) carry[lc] = has_c ? st[c] : 0.f;
+
+    float l_r[PER], l_i[PER], l_u[PER], l_y[PER];
+    auto load_tile = [&](int t0) {
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            const int t = t0 + lt + j * ROWS;
+            if (has_c && t < qlen) {
+                const size_t tok = (size_t)(q0 + t);
+                l_r[j] = pr[(size_t)t * bw];
+                l_i[j] = pr[(size_t)t * bw + gate_i];
+                l_u[j] = to_f32<T>(u[tok * C + c]);
+                l_y[j] = to_f32<T>(y[tok * ldy + c]);
+            }
+        }
+    };
+    load_tile(0);
+    for (int t0 = 0; t0 < qlen; t0 += LRU_T) {
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            const int tl = lt + j * ROWS;
+            float a = 1.f, b = 0.f, g = 0.f;   // a token past the end leaves the state as it is
+            if (has_c && t0 + tl < qlen) {
+                const float r = sigmoid_f(l_r[j] + rb);
+                const float ig = sigmoid_f(l_i[j] + ib);
+                const float log_a = -sp * r;
+                a = expf(log_a);
+                b = sqrtf(-expm1f(2.f * log_a)) * ig * l_u[j];   // sqrt(1 - a^2) without the cancellation
+                g = y_act ? gelu_tanh_f(l_y[j]) : l_y[j];
+            }
+            sa[tl][lc] = a;
+            sb[tl][lc] = b;
+            sg[tl][lc] = g;
+        }
+        __syncthreads();
+        if (t0 + LRU_T < qlen) load_tile(t0 + LRU_T);   // in flight during the scan
+        // a warp per channel, a lane per token
+#pragma unroll
+        for (int j = 0; j < LRU_C / LRU_W; ++j) {
+            const int ch = warp + j * LRU_W;
+            float A = sa[lane][ch], B = sb[lane][ch];
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const float Ap = __shfl_up_sync(0xffffffffu, A, off), Bp = __shfl_up_sync(0xffffffffu, B, off);
+                if (lane >= off) {
+                    B = fmaf(A, Bp, B);
+                    A *= Ap;
+                }
+            }
+            const float S = fmaf(A, carry[ch], B);
+            sb[lane][ch] = S;
+            __syncwarp();
+            if (lane == 31) carry[ch] = S;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            const int tl = lt + j * ROWS;
+            if (has_c && t0 + tl < qlen) out[(size_t)(q0 + t0 + tl) * C + c] = from_f32<T>(sb[tl][lc] * sg[tl][lc]);
+        }
+        __syncthreads();
     }
-    *sp_state = S;
+    if (threadIdx.x < LRU_C && has_c) st[c] = carry[lc];
+}
+
+// A step in which every request brings one token: a thread owns (request, channel).
+template <typename T>
+__global__ void rglru_step_kernel(const T* __restrict__ u, const float* __restrict__ pre, const void* __restrict__ br,
+                                  const void* __restrict__ bi, const void* __restrict__ lam, int p_dtype,
+                                  const T* __restrict__ y, long long ldy, int y_act, float cmul,
+                                  float* __restrict__ state, const int* __restrict__ slots, T* __restrict__ out,
+                                  int N, int C, int blocks) {
+    const int tok = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int bw = C / blocks;
+    const size_t at = ((size_t)(c / bw) * N + tok) * bw + c % bw;
+    const float r = sigmoid_f(pre[at] + load_any(br, p_dtype, c));
+    const float ig = sigmoid_f(pre[at + (size_t)N * C] + load_any(bi, p_dtype, c));
+    const float log_a = -cmul * softplus_f(load_any(lam, p_dtype, c)) * r;
+    float* sp = state + (size_t)slots[tok] * C + c;
+    const float S = fmaf(expf(log_a), *sp, sqrtf(-expm1f(2.f * log_a)) * ig * to_f32<T>(u[(size_t)tok * C + c]));
+    *sp = S;
+    float yy = to_f32<T>(y[(size_t)tok * ldy + c]);
+    if (y_act) yy = gelu_tanh_f(yy);
+    out[(size_t)tok * C + c] = from_f32<T>(S * yy);
 }
 
 }  // namespace ems
@@ -302,8 +547,8 @@ EMS_EXPORT int ems_matrix_recurrence(const void* q, long long ldq, const void* k
     p.denom_floor = denom_floor; p.denom = denom; p.state = state; p.slots = slots; p.cu_q = cu_q; p.out = out;
     p.H = H; p.D = D; p.V = V; p.head_stride = head_stride; p.normaliser = normaliser; p.act = act;
     p.q_scale = q_scale; p.denom_eps = denom_eps;
-    if (dtype == EMS_F32) return launch_matrix_recurrence<float>(p, rows, stream);
-    if (dtype == EMS_BF16) return launch_matrix_recurrence<bf16>(p, rows, stream);
+    if (dtype == EMS_F32) return launch_matrix_recurrence<float>(p, rows, N, stream);
+    if (dtype == EMS_BF16) return launch_matrix_recurrence<bf16>(p, rows, N, stream);
     return EMS_ERR_DTYPE;
 }
 
@@ -347,8 +592,20 @@ EMS_EXPORT int ems_rglru_scan(const void* u, const float* pre, const void* br, c
                               int blocks, cudaStream_t stream) {
     if (rows <= 0 || N <= 0) return EMS_OK;
     if (blocks <= 0 || C % blocks || rows > 65535) return EMS_ERR_SHAPE;
-    const int th = C >= 128 ? 128 : 32 * ((C + 31) / 32);
-    const dim3 grid((C + th - 1) / th, rows);
+    if (N == rows) {   // every request brings one token (the state of a request is independent of its row's index)
+        const dim3 sgrid((C + 127) / 128, rows);
+        if (dtype == EMS_F32)
+            rglru_step_kernel<float><<<sgrid, 128, 0, stream>>>((const float*)u, pre, br, bi, lam, p_dtype, (const float*)y,
+                                                                ldy, y_act, cmul, state, slots, (float*)out, N, C, blocks);
+        else if (dtype == EMS_BF16)
+            rglru_step_kernel<bf16><<<sgrid, 128, 0, stream>>>((const bf16*)u, pre, br, bi, lam, p_dtype, (const bf16*)y,
+                                                               ldy, y_act, cmul, state, slots, (bf16*)out, N, C, blocks);
+        else
+            return EMS_ERR_DTYPE;
+        return launch_status();
+    }
+    const int th = LRU_W * 32;
+    const dim3 grid((C + LRU_C - 1) / LRU_C, rows);
     if (dtype == EMS_F32)
         rglru_scan_kernel<float><<<grid, th, 0, stream>>>((const float*)u, pre, br, bi, lam, p_dtype, (const float*)y,
                                                           ldy, y_act, cmul, state, slots, cu_q, (float*)out, N, C,
