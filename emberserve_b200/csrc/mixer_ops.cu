@@ -17,17 +17,31 @@ namespace ems {
 #define EMS_ACT_GELU_TANH 2
 #define EMS_ACT_SILU 3
 
+__device__ __forceinline__ float unary_activation(float z, int act) {
+    if (act == EMS_ACT_RELU) return fmaxf(z, 0.f);
+    if (act == EMS_ACT_RELU2) { const float r = fmaxf(z, 0.f); return r * r; }
+    if (act == EMS_ACT_GELU_TANH) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    return z / (1.f + expf(-z));
+}
+
 template <typename T>
 __global__ void unary_act_kernel(const T* __restrict__ x, T* __restrict__ out, size_t n, int act) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
-    const float z = to_f32<T>(x[i]);
-    float y;
-    if (act == EMS_ACT_RELU) y = fmaxf(z, 0.f);
-    else if (act == EMS_ACT_RELU2) { const float r = fmaxf(z, 0.f); y = r * r; }
-    else if (act == EMS_ACT_GELU_TANH) y = 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
-    else y = z / (1.f + expf(-z));
-    out[i] = from_f32<T>(y);
+    out[i] = from_f32<T>(unary_activation(to_f32<T>(x[i]), act));
+}
+
+// 16 bytes per thread and trip, where the buffers begin on a 16-byte boundary
+template <typename T>
+__global__ void unary_act_vec_kernel(const uint4* __restrict__ x, uint4* __restrict__ out, size_t nvec, int act) {
+    constexpr int PER = 16 / sizeof(T);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
+        uint4 v = x[i];
+        T* e = reinterpret_cast<T*>(&v);
+#pragma unroll
+        for (int j = 0; j < PER; ++j) e[j] = from_f32<T>(unary_activation(to_f32<T>(e[j]), act));
+        out[i] = v;
+    }
 }
 
 // One block per token, one warp per head at a time (query heads, then key heads).  proj row:
@@ -116,6 +130,16 @@ using namespace ems;
 EMS_EXPORT int ems_unary_act(const void* x, void* out, int dtype, long long n, int act, cudaStream_t stream) {
     if (n <= 0) return EMS_OK;
     if (act < 0 || act > 3) return EMS_ERR_SHAPE;
+    const int per = dtype == EMS_F32 ? 4 : 8;
+    if ((dtype == EMS_F32 || dtype == EMS_BF16) && n % per == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)out % 16) == 0) {
+        const size_t nvec = (size_t)(n / per);
+        const unsigned vblocks = (unsigned)((nvec + 255) / 256 < 148 * 16 ? (nvec + 255) / 256 : 148 * 16);
+        if (dtype == EMS_F32)
+            unary_act_vec_kernel<float><<<vblocks, 256, 0, stream>>>((const uint4*)x, (uint4*)out, nvec, act);
+        else
+            unary_act_vec_kernel<bf16><<<vblocks, 256, 0, stream>>>((const uint4*)x, (uint4*)out, nvec, act);
+        return launch_status();
+    }
     const unsigned blocks = (unsigned)((n + 255) / 256);
     if (dtype == EMS_F32) unary_act_kernel<float><<<blocks, 256, 0, stream>>>((const float*)x, (float*)out, (size_t)n, act);
     else if (dtype == EMS_BF16) unary_act_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)x, (bf16*)out, (size_t)n, act);

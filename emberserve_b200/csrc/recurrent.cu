@@ -39,7 +39,7 @@ __device__ __forceinline__ float in_act(float z, int act) { return act == EMS_IN
 // normaliser) for one request.  A column is shared by SL lanes (32, 16 or 8, by the head's rows D);
 // lane s holds rows i * 4 SL + 4 s + e (e < 4, i < DPT / 4) of the column of S in registers, so that
 // the lanes of a warp read a staged q or k row as consecutive float4 and the dot product with q
-// closes with log2(SL) shuffles.  The step's tokens are staged in tiles: q (scaled) and k (times
+// closes with shuffles among those lanes, once per tile.  The step's tokens are staged in tiles: q (scaled) and k (times
 // b_t) widened and passed through the activation once; rows past D are zero.  A tile's inputs are
 // asked for, as they lie in memory, while the tile before is computed, and widened when staged.
 // Per token a thread does DPT multiply-adds into S and DPT into the read; only S carries from token
@@ -200,13 +200,18 @@ __global__ void __launch_bounds__(MR_WARPS * 32) matrix_recurrence_kernel(const 
             }
         }
         if ((int)threadIdx.x < TT) {
-            as[threadIdx.x] = ra;
+            as[threadIdx.x] = (int)threadIdx.x < cnt ? ra : 1.f;
             fs[threadIdx.x] = rf;
         }
         __syncthreads();
         if (t0 + TT < qlen) ask(t0 + TT);   // in flight while this tile is computed
-#pragma unroll 2
-        for (int t = 0; t < cnt; ++t) {
+        // every token of the tile (tokens past the end are staged as "decay 1, nothing added"); a lane
+        // keeps its share of each token's read, and the shares are summed over the SL lanes of a
+        // column once per tile: log2(SL) rounds in which a lane hands one half of what it holds to
+        // its partner and adds the partner's other half, 31 shuffles for 32 tokens instead of 160
+        float acc[TT];
+#pragma unroll
+        for (int t = 0; t < TT; ++t) {
             const float a = as[t];
             const float vj = vs[t * COLS + lcol];
             const float4* k4 = reinterpret_cast<const float4*>(ks + t * DP) + slice;
@@ -224,13 +229,28 @@ __global__ void __launch_bounds__(MR_WARPS * 32) matrix_recurrence_kernel(const 
                 acc2 = fmaf(S[4 * i + 2], qq.z, acc2);
                 acc3 = fmaf(S[4 * i + 3], qq.w, acc3);
             }
-            float acc = (acc0 + acc1) + (acc2 + acc3);
+            acc[t] = (acc0 + acc1) + (acc2 + acc3);
+        }
 #pragma unroll
-            for (int off = 1; off < SL; off <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-            if (live && slice == 0) {
-                const size_t tok = (size_t)(q0 + t0 + t);
-                if (is_norm) p.denom[tok * p.H + head] = fmaxf(fabsf(acc), fs[t]) + p.denom_eps;
-                else p.out[tok * ((size_t)p.H * V) + (size_t)head * V + col] = acc;
+        for (int off = SL / 2, n = TT; off >= 1; off >>= 1, n >>= 1) {
+            const bool upper = (lane & off) != 0;
+#pragma unroll
+            for (int j = 0; j < n / 2; ++j) {
+                const float send = upper ? acc[j] : acc[j + n / 2];
+                const float keep = upper ? acc[j + n / 2] : acc[j];
+                acc[j] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+            }
+        }
+        // lane `slice` of a column now holds the tokens [slice * TT / SL, (slice + 1) * TT / SL) of the tile
+        if (live) {
+#pragma unroll
+            for (int j = 0; j < TT / SL; ++j) {
+                const int t = slice * (TT / SL) + j;
+                if (t < cnt) {
+                    const size_t tok = (size_t)(q0 + t0 + t);
+                    if (is_norm) p.denom[tok * p.H + head] = fmaxf(fabsf(acc[j]), fs[t]) + p.denom_eps;
+                    else p.out[tok * ((size_t)p.H * V) + (size_t)head * V + col] = acc[j];
+                }
             }
         }
     }
@@ -296,8 +316,11 @@ static int launch_matrix_recurrence_as(const MatRecParams& p, int rows, cudaStre
     const int ncols = p.V + (p.normaliser ? 1 : 0);
     const dim3 grid((ncols + COLS - 1) / COLS, p.H, rows);
     const size_t smem = sizeof(float) * ((size_t)TT * (2 * SL * DPT + COLS) + 2 * TT);
-    if (p.vec_ok) matrix_recurrence_kernel<T, DPT, SL, TT, true><<<grid, MR_WARPS * 32, smem, stream>>>(p);
-    else matrix_recurrence_kernel<T, DPT, SL, TT, false><<<grid, MR_WARPS * 32, smem, stream>>>(p);
+    auto kernel = p.vec_ok ? matrix_recurrence_kernel<T, DPT, SL, TT, true> : matrix_recurrence_kernel<T, DPT, SL, TT, false>;
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return EMS_ERR_LAUNCH;
+    kernel<<<grid, MR_WARPS * 32, smem, stream>>>(p);
     return launch_status();
 }
 
@@ -316,8 +339,7 @@ static int launch_matrix_recurrence(MatRecParams& p, int rows, int N, cudaStream
     if (p.D <= 32) return launch_matrix_recurrence_as<T, 4, 8, 32>(p, rows, stream);
     if (p.D <= 64) return launch_matrix_recurrence_as<T, 4, 16, 32>(p, rows, stream);
     if (p.D <= 128) return launch_matrix_recurrence_as<T, 4, 32, 32>(p, rows, stream);
-    if (p.D <= 256) return launch_matrix_recurrence_as<T, 8, 32, 16>(p, rows, stream);
-    return EMS_ERR_SHAPE;
+    return launch_matrix_recurrence_as<T, 8, 32, 32>(p, rows, stream);
 }
 
 // ---------------------------------------------------------------------------------------
