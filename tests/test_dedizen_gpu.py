@@ -206,13 +206,14 @@ def test_masked_attention_against_dense(dtype, nh, nkv, d, ps, chunk, window):
 
 
 @DTYPES
+@pytest.mark.parametrize("d", [16, 128], ids=["generic", "tensor-core-size"])
 @pytest.mark.parametrize("decode", [False, True], ids=["prompt", "decoded"])
-def test_a_planted_key_shows_at_chunk_and_page_edges(dtype, decode):
+def test_a_planted_key_shows_at_chunk_and_page_edges(dtype, decode, d):
     """One key is made to win the softmax (its dot product with one query stands out) and its value
     is a one-hot: the output shows whether the query saw it.  Chunks of 48 over pages of 16: the
     first key of the query's chunk (also the first of a page) is seen, the last key of the chunk
     before is not; a key far back in the same chunk across three pages is; the query itself is."""
-    nh, nkv, d, ps, chunk = 2, 1, 16, 16, 48
+    nh, nkv, ps, chunk = 2, 1, 16, 48
     g = torch.Generator().manual_seed(5)
     qpos = 48 * 3 + 40  # position 184, chunk 144..191
     for key, seen in ((144, True), (143, False), (145, True), (160, True), (184, True), (0, False), (96, False)):
@@ -228,10 +229,10 @@ def test_a_planted_key_shows_at_chunk_and_page_edges(dtype, decode):
         vc[page, 0, slot] = 0
         vc[page, 0, slot, 3] = 50.0
         case[4], case[5] = kc.to(dtype), vc.to(dtype)
-        out = _run_attention(case, nh, nkv, d, 0.25, qlen, 1, chunk, None, False, False)
+        out = _run_attention(case, nh, nkv, d, 4.0 / d, qlen, 1, chunk, None, False, False)
         got = float(out[row, 3])
         assert (got > 40.0) == seen, f"key {key} from position {qpos}: {got}"
-        want = _run_attention(case, nh, nkv, d, 0.25, qlen, 1, chunk, None, False, False, dev=False)
+        want = _run_attention(case, nh, nkv, d, 4.0 / d, qlen, 1, chunk, None, False, False, dev=False)
         _close(out, want, dtype, f"key {key}")
 
 
@@ -391,6 +392,7 @@ def test_gated_diagonal_recurrence_in_portions(dtype, c, blocks):
 
 ONE_MIXER = {
     "attention": td._parallel(td._left(4, 2, 16, 6, 8, 1000.0, (2.0, 8, 2.0, 0.5)), td._right(1, 4, 4, (0.9,)), None),
+    "attention_64": td._parallel(td._left(4, 2, 64, 20, 32, 5000.0, (4.0, 32, 8.0, 1.0)), td._right(1, 4, 4, (0.9,)), None),
     "memory": td._parallel(td._left(1, 1, 8, 2, 0, 0.0), td._right(3, 10, 12, (0.4, 0.9, 0.995)), None),
     "mlstm": td._mlstm(2, 12, 20, 3.0, None),
     "rglru": td._rglru(48, 4, 4, None),
