@@ -346,8 +346,8 @@ static int launch_matrix_recurrence(MatRecParams& p, int rows, int N, cudaStream
 // the gates of the mLSTM: log input gate i = cap tanh(x_i / cap), log forget gate f =
 // logsigmoid(cap tanh(x_f / cap)), running maximum m_t = max(f + m_(t-1), i) (m starts at 0 in a
 // fresh slot), a_t = exp(f + m_(t-1) - m_t), b_t = exp(i - m_t), floor_t = exp(-m_t).
-// One warp per (request, head): the lanes take 32 tokens' transcendental work side by side, the
-// maximum runs through them in order.
+// One warp per (request, head): the lanes take 32 tokens' transcendental work side by side, and the
+// maximum runs through them as a scan of the maps m -> max(f + m, i).
 
 __global__ void mlstm_gates_kernel(const float* __restrict__ pre, const void* __restrict__ bias_i,
                                    const void* __restrict__ bias_f, int b_dtype, float cap,
@@ -372,13 +372,22 @@ __global__ void mlstm_gates_kernel(const float* __restrict__ pre, const void* __
             ig = cap > 0.f ? cap * tanhf(xi / cap) : xi;
             fg = logsigmoid_f(cap > 0.f ? cap * tanhf(xf / cap) : xf);
         }
-        float before = 0.f, after = 0.f;
-        for (int j = 0; j < cnt; ++j) {
-            const float fj = __shfl_sync(0xffffffffu, fg, j), ij = __shfl_sync(0xffffffffu, ig, j);
-            const float m_new = fmaxf(fj + m, ij);
-            if (lane == j) { before = m; after = m_new; }
-            m = m_new;
+        // m_t = max(f_t + m_(t-1), i_t) is the map m -> max(F + m, I) with (F, I) = (f_t, i_t); maps
+        // compose as (F1, I1) then (F2, I2) = (F1 + F2, max(I1 + F2, I2)): a scan over the lanes.
+        // (A lane past the end holds the identity (0, -inf).)
+        float F = lane < cnt ? fg : 0.f, I = lane < cnt ? ig : -INFINITY;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const float Fp = __shfl_up_sync(0xffffffffu, F, off), Ip = __shfl_up_sync(0xffffffffu, I, off);
+            if (lane >= off) {
+                I = fmaxf(Ip + F, I);
+                F += Fp;
+            }
         }
+        const float after = fmaxf(F + m, I);
+        float before = __shfl_up_sync(0xffffffffu, after, 1);
+        if (lane == 0) before = m;
+        m = __shfl_sync(0xffffffffu, after, cnt - 1);
         if (lane < cnt) {
             const size_t at = (size_t)(q0 + t0 + lane) * H + head;
             a_out[at] = expf(fg + before - after);

@@ -303,7 +303,8 @@ __global__ void causal_taps_single_kernel(const T* __restrict__ x, long long ldx
                                           T* __restrict__ out, int C, int taps) {
     const int row = blockIdx.x;
     float* st = state + (size_t)slots[row] * (taps - 1) * C;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    // (blocks along y share a row's channels, so that a wide row is not one block's loop)
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
         const float h = to_f32<T>(x[(size_t)row * ldx + c]);
         float conv = bias ? load_any(bias, w_dtype, c) : 0.f;
         for (int j = 0; j < taps - 1; ++j) {
@@ -415,7 +416,8 @@ EMS_EXPORT int ems_causal_taps(const void* x, long long ldx, const void* w, int 
 #define EMS_LAUNCH_TAPS(T)                                                                                   \
     do {                                                                                                     \
         if (n == rows && taps > 1) {                                                                         \
-            causal_taps_single_kernel<T><<<rows, th, 0, stream>>>((const T*)x, ldx, w, w_dtype, bias,        \
+            causal_taps_single_kernel<T><<<dim3(rows, (C + th - 1) / th), th, 0, stream>>>(                  \
+                                                                  (const T*)x, ldx, w, w_dtype, bias,        \
                                                                   identity, (float*)state,                   \
                                                                   slots, (T*)out, C, taps);                  \
             break;                                                                                           \
