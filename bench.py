@@ -960,11 +960,11 @@ def dedizen_config(size: str, vocab: int = 32000) -> dict:
     parallel = {"type": "parallel", "mlp": mlp, "mixer": {
         "left": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
                  "mask": {"size": z["chunk"]}, "scale": z["dim"] ** -0.5,
-                 "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0,
-                                                                    "slow": 1.0}}},
+                 "rot": {"base": 1000000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 8192, "fast": 16.0,
+                                                                     "slow": 2.0}}},
         "right": {"heads": mh, "dim": md, "vdim": mv, "decay": [1.0 - 2.0 ** (-5 - 3 * h / mh) for h in range(mh)]}}}
     xh, xd, xv = z["mlstm"]
-    mlstm = {"type": "mlstm", "mlp": mlp, "mixer": {"heads": xh, "dim": xd, "vdim": xv, "gate_cap": 15.0}}
+    mlstm = {"type": "mlstm", "mlp": mlp, "mixer": {"heads": xh, "dim": xd, "vdim": xv, "gate_cap": 10.0}}
     rglru = {"type": "rglru", "mlp": mlp, "mixer": {"width": z["lru"], "blocks": z["lru_blocks"], "conv": 4}}
     return {"architecture": "Dedizen", "vocab": vocab, "width": z["width"], "norm": {"eps": 1e-5},
             "layers": [parallel, mlstm, rglru, rglru, parallel, mlstm], "max_positions": 8192}
